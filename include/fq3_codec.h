@@ -48,7 +48,8 @@ enum fq3c_kind {
    * Unless said otherwise A is f32 [M, lda], the output is bf16 or, with FQ3C_OUT_F32, f32; weights (B) are bf16 or, with
    * FQ3C_F32, f32.  Per-sequence state lives in caller-owned buffers; the position counter is a device int32 (p0) so that a
    * captured list replays at any position. */
-  FQ3C_EMBED = 12,    /* C f32 [M, N] = B[ids[m], :]; A = device int32 ids [M]                                                */
+  FQ3C_EMBED = 12,    /* C f32 [M, N] = B[ids[m], :]; A = device int32 ids [M].  ABI 8: f0 != 0 multiplies the row; i0 > 1 writes i0
+                         equal copies, copy s at C + s * K elements (the residual streams of FQ3C_HYPER at a sequence's start)      */
   FQ3C_TCONV = 13,    /* causal per-channel convolution over time with carried inputs: C[m, c] = (RESID ? A[m, c] : 0) + bias[c] +
                          sum_j B(f32 [N, taps])[c, j] * in[m - (taps - 1) + j, c], where rows before this call come from the history
                          p0 (f32 [taps - 1, N], oldest first; zeros at a sequence's start).  The next history (the last taps - 1
@@ -63,7 +64,11 @@ enum fq3c_kind {
                          space f32 [M, i0 heads * i1 rank]; B = latent cache [>= *p0 + M rows, ldr] (bf16, F32: f32); query m sees
                          rows [0, *p0 + m]; score = f0 * (q . c); softmax whose denominator also holds exp(scale[h]) (a per-head sink
                          without key or value; scale = f32 [i0], may be NULL); C f32 [M, i0 * i1] = sum_j p_j c_j.  i2 = heads per
-                         block; K = key-range splits (> 1: ws holds the partial states and a second launch merges them)           */
+                         block; K = key-range splits (> 1: ws holds the partial states and a second launch merges them).
+                         ABI 8: cin = E > 0: a cache row holds E more columns behind the i1 latent ones (a rotated key part shared by
+                         all heads) that enter the score only; their queries are p1 = f32 [M, taps], head h at column h * E (already
+                         rotated), so score = f0 * (q . c + q_E . k_E).  a_rows = W > 0: sliding window, query at position i sees
+                         i - W < j <= i.  res = f32 [M, m_begin], when given: head h's output is multiplied by sigmoid(res[m, h])     */
   FQ3C_LRU_SCAN = 17, /* gated diagonal linear recurrence, 32-bit state: per channel c and row t, with gates g = A f32 [M, lda]
                          (recurrence gate r at column c, input gate i at column N + c, already sigmoid), input u = B f32 [M, cin],
                          branch y = res f32 [M, ldr] (before its activation), lam = scale f32 [N]:
@@ -76,6 +81,7 @@ enum fq3c_kind {
                          NULL); experts form i1 equal groups of neighbours, a group's score is its largest choice, only the best i2
                          groups stay eligible; the i0 largest eligible choices are taken (lower index wins a tie);
                          weights = s[chosen] / (sum + 1e-20) * f0.  C = int32 [M, i0] expert ids, C2 = f32 [M, i0] weights.
+                         ABI 8: FQ3C_SIGMOID: s = sigmoid(logit) instead of the softmax; FQ3C_RAW_WEIGHTS: weights = s[chosen] * f0.
                          With ws set (M = 1, i0 <= 16) the launch also does FQ3C_MOE_SORT's grouping: K = experts that are real,
                          p0 = segment starts, p1 = token of each sorted position, ws = sorted position of each choice or -1     */
   FQ3C_MOE_SORT = 20, /* A = int32 ids [M, i0]; experts with id < i1 are real.  C = int32 [i1 + 1] segment starts, C2 = int32
@@ -86,7 +92,8 @@ enum fq3c_kind {
                          NULL, i0 experts, M = upper bound of positions.  A bf16, or f32 with FQ3C_A_F32; B bf16, F32: both f32     */
   FQ3C_MOE_COMBINE = 22, /* C f32 [M, N] = sum_j w[m, j] * (ids[m, j] >= i1 ? x[m, :] : Y[pos[m, j], :]) (+ res[m, :]);
                          A = Y f32, B = x f32 [M, ldr] (identity experts), p0 = ids int32 [M, i0], p1 = w f32 [M, i0],
-                         ws = pos int32 [M, i0], res = f32 [M, ldr] or NULL (shared expert)                                      */
+                         ws = pos int32 [M, i0], res = f32 [M, ldr] or NULL (shared expert).  ABI 8: p1 may be NULL (every w = 1:
+                         experts whose weight was applied to their input)                                                        */
   FQ3C_COMMIT = 23,   /* end of a step: A = device int64 [M, 3] rows (dst, src, bytes), bytes a multiple of 4, copied in one launch;
                          then *(int32*)C += i0 (the sequence's position counter)                                               */
   /* ---- ABI 7: more mechanisms of the sequence models (same conventions as kinds 12-23) */
@@ -103,7 +110,11 @@ enum fq3c_kind {
                          Row m is position *p0 + m.  The first `taps` entries of every query and key head turn in pairs (2i, 2i + 1)
                          by the angle position * B[i] (B = f32 [taps / 2] frequencies; taps = 0: no rotation); queries in place,
                          keys into row *p0 + m of the key cache C (pitch ldc), values into the value cache C2 (pitch ldr); caches
-                         bf16, or f32 with FQ3C_F32.  i1 = 0: queries only (a layer that reads another layer's cache)               */
+                         bf16, or f32 with FQ3C_F32.  i1 = 0: queries only (a layer that reads another layer's cache).
+                         ABI 8: f1 != 0 multiplies both cos and sin (the amplitude of a scaled rotary table); res, when given
+                         (f32 [M, norm_ld]): the key and value heads are read from these rows (columns K / a_rows) instead of A;
+                         scale / bias (f32 [i2]), when given: every query / key head is RMS-normed over its i2 entries (eps f0)
+                         and multiplied by these weights before it turns; cin = 0: no values                                       */
   FQ3C_CACHE_ATTN = 28, /* softmax attention of M new queries over a key / value cache.  A = queries f32 [M, lda] (i0 heads of size i2),
                          B = key cache rows [i1 heads * i2] of pitch ldr, p1 = value cache rows [i1 heads * cin] of pitch taps
                          (bf16, F32: f32); query head h reads key / value head h / (i0 / i1); query m has position i = *p0 + m
@@ -112,7 +123,8 @@ enum fq3c_kind {
                          given: score -= r1[h] ln(1 + r2[h] (i - j)); scale (f32 [i0]), when given: a per-head sink that only adds
                          exp(scale[h]) to the softmax denominator; res (f32 [M, col_mod]), when given: head h's output is multiplied
                          by sigmoid(res[m, h]).  C [M, i0 * cin].  m_begin = key-range splits (> 1: ws holds the partial states and
-                         a second launch merges them)                                                                              */
+                         a second launch merges them).  ABI 8: tap_off[0] = S > 0: chunked mask, j must also lie in i's chunk
+                         (j >= i - i % S; chunks count from position 0 of the sequence)                                            */
   FQ3C_MSTATE_SCAN = 29 /* recurrences whose state is a matrix S [i2, cin] per head (i0 heads, i1 key groups; head h reads group
                          h / (i0 / i1)), 32-bit.  A = f32 rows [M, lda] after the short convolution: taps = 0 (gated delta rule):
                          queries of group g at column g * i2, keys at column K + g * i2, values of head h at a_rows + h * cin;
@@ -124,7 +136,17 @@ enum fq3c_kind {
                              g = exp(-exp(A_log) softplus(a + dt_bias));  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
                            scan: dt = softplus(dt + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  o = S^T C + D x
                          State read from p0 (f32 [i0, i2, cin]), next state written to C2 (FQ3C_COMMIT installs it); C f32 [M, i0 * cin];
-                         ws = f32 [M, round_up(2 * i0 + (taps == 0 ? 2 * i1 * i2 + i1 : 0), 4)]: unit vectors, coefficients, q.k       */
+                         ws = f32 [M, round_up(2 * i0 + (taps == 0 ? 2 * i1 * i2 + i1 : 0), 4)]: unit vectors, coefficients, q.k       */,
+  /* ---- ABI 8 */
+  FQ3C_HYPER = 30,    /* several residual streams (hyper-connections): X_s = A + s * K elements, s < i0 <= 8 (f32 slices [M, lda] of one
+                         buffer).  With res (y = f32 [M, ldr], a sublayer's output): every stream at once from the old ones,
+                         X_t <- sum_s p0[s * i0 + t] X_s + f1 * p1[t] * y  (p0 = f32 [i0, i0] indexed [from, to], p1 = f32 [i0]).
+                         Then, with C: u = sum_s bias[s] X_s (bias = f32 [i0], the next sublayer's read weights) and
+                         C[m, :] = u / sqrt(mean(u^2) + f0) * scale (scale = f32 [N]; bf16, or f32 with FQ3C_OUT_F32), or, when scale
+                         is NULL, C f32 = u itself (the sum of the streams with bias = ones)                                          */
+  FQ3C_GLU = 31       /* gated unit over rows that hold [gate | up]: C[r, c] = silu(w A[r, c]) * (w A[r, N + c]), c < N, A f32 [.., lda];
+                         row r = ws[q] (int32 [M], a negative entry skips the row) or q itself, w = p1[q] (f32 [M]) or 1: with both,
+                         q runs over the (token, choice) pairs of a router and w is the choice's weight, applied to the expert's input */
 };
 
 enum fq3c_flags {
@@ -139,7 +161,9 @@ enum fq3c_flags {
   FQ3C_A_F32 = 8192     /* GGEMM: A rows are f32 while B is bf16 */,
   /* ABI 7 */
   FQ3C_GATE_PRE = 16384 /* GNORM: the row is multiplied by silu(p1[m, c]) (f32, pitch i1) before its statistics are taken */,
-  FQ3C_GATE_POST = 32768 /* GNORM: the normed, weighted row is multiplied by silu(p1[m, c]) */
+  FQ3C_GATE_POST = 32768 /* GNORM: the normed, weighted row is multiplied by silu(p1[m, c]) */,
+  /* ABI 8 */
+  FQ3C_RAW_WEIGHTS = 65536 /* ROUTER: the chosen scores are the weights (times f0), not divided by their sum */
 };
 
 typedef struct fq3c_op {

@@ -244,10 +244,19 @@ class LatentAttentionConfig:
     cached), without positional rotation, with a learned per-head sink in the softmax denominator."""
 
     heads: int
-    dim: int        # query / key size per head
+    dim: int        # query / key size per head (the part without rotation)
     vdim: int       # value size per head
     kv_rank: int    # latent size
     scale: float    # multiplies q . k
+    # options (all off: the plain form above)
+    q_rank: int = 0          # > 0: queries go through a normed latent of this size too
+    rot_dim: int = 0         # > 0: every query head has this many more entries that turn with the position, scored against one
+                             #      rotated key part per position shared by all heads (cached beside the latent)
+    rot_base: float = 10000.0
+    rot_scaling: Optional[Tuple[float, float, float, float]] = None   # (factor, original, fast, slow): scaled rotary table
+    window: int = 0          # > 0: position i sees j only if 0 <= i - j < window
+    gate: bool = False       # one sigmoid gate per head on the head's output
+    sink: bool = True        # a per-head sink tensor may be present
 
 
 @dataclass(frozen=True)
@@ -275,6 +284,10 @@ class MoEFFConfig:
     scale: float        # multiplies the normalised weights
     expert_ff: int
     shared_ff: int      # 0: no shared expert
+    score: str = "softmax"       # "softmax" over all outputs | "sigmoid" of each logit
+    renorm: bool = True          # weights = chosen scores / their sum (times scale); False: the chosen scores themselves
+    weight_input: bool = False   # the weight multiplies the expert's input instead of its output
+    gated: bool = False          # expert = W_down (silu(W_gate x) * W_up x) instead of W_down gelu(W_up x); the shared one too
 
     @property
     def routed(self) -> int:
@@ -354,6 +367,9 @@ class SoftmaxAttentionConfig:
     bias: bool = False       # q, k, v and output projections have biases
     distance: bool = False   # score -= r1_h ln(1 + r2_h (i - j))
     kv_from: Optional[int] = None   # index of the layer whose cached keys / values this layer reads
+    chunk: int = 0           # > 0: position i sees j only inside its own chunk (i // chunk == j // chunk), chunks from position 0
+    qk_norm: bool = False    # queries and keys are RMS-normed per head (one weight vector each, shared by the heads)
+    zero_sink: bool = False  # a sink of score 0 without a tensor: the softmax denominator holds one more 1
 
 
 @dataclass(frozen=True)
@@ -442,10 +458,74 @@ class RedodraConfig:
         return RedodraConfig(int(raw["vocab"]), int(raw["width"]), float((raw.get("norm") or {}).get("eps", 1e-6)), tuple(layers))
 
 
+@dataclass(frozen=True)
+class RatizenConfig:
+    """Ratizen: several residual streams with learned read / write / mixing weights around every sublayer (hyper-connections),
+    one-plus RMS norms in front of the sublayers, chunked attention with per-head query / key norms and a zero-score sink,
+    windowed latent attention with a shared rotary key part (scaled rotary table) and an output gate, in a configured order;
+    feed-forwards of sigmoid-routed gated experts whose weight multiplies their input, plus a shared expert."""
+
+    architecture = "Ratizen"
+    vocab: int
+    width: int
+    norm_eps: float
+    embed_scale: float
+    residual_mult: float            # multiplies every sublayer's output on its way into the streams
+    streams: int
+    hyper: bool                     # the checkpoint holds read / write / mixing weights (else: one plain residual stream)
+    logit_scale: float
+    layers: Tuple[SeqLayerConfig, ...]
+
+    @staticmethod
+    def from_dict(raw: dict) -> "RatizenConfig":
+        layers = []
+        for i, L in enumerate(raw["layers"]):
+            m = L["mixer"]
+            mask = m.get("mask") or {}
+            if L["type"] == "attention":
+                mixer = SoftmaxAttentionConfig(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"]), float(m["scale"]),
+                                               chunk=int(mask.get("size", 0)), qk_norm=True, zero_sink=True)
+                if mixer.heads % mixer.kv_heads:
+                    raise ValueError(f"layer {i}: kv_heads must divide heads")
+            elif L["type"] == "latent_attention":
+                rot = m.get("rot") or {}
+                sc = rot.get("scaling")
+                rot_dim = int(m.get("rot_dim", 0))
+                if rot_dim and int(rot.get("dims", rot_dim)) != rot_dim:
+                    raise ValueError(f"layer {i}: the rotary table must cover the whole rotated part")
+                if rot_dim % 2:
+                    raise ValueError(f"layer {i}: rot_dim must be even")
+                mixer = LatentAttentionConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"]),
+                                              q_rank=int(m.get("q_rank", 0)), rot_dim=rot_dim, rot_base=float(rot.get("base", 10000.0)),
+                                              rot_scaling=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None,
+                                              window=int(mask.get("size", 0)), gate=True, sink=False)
+            else:
+                raise ValueError(f"unknown mixer type {L['type']!r}")
+            f = L.get("mlp")
+            if f is None:
+                mlp = None
+            elif f.get("kind", "moe") == "moe":
+                r, sh = f["router"], f.get("shared")
+                mlp = MoEFFConfig(int(r["experts"]), 0, int(r["top"]), 1, 1, 1.0, int(f["expert"]["ff"]), int(sh["ff"]) if sh else 0,
+                                  score="sigmoid", renorm=False, weight_input=True, gated=True)
+                if not 1 <= mlp.top <= mlp.experts:
+                    raise ValueError(f"layer {i}: top must lie in 1 .. experts")
+            else:
+                raise ValueError(f"unknown feed-forward kind {f['kind']!r}")
+            layers.append(SeqLayerConfig(L["type"], mixer, mlp))
+        streams = int(raw.get("streams", 1))
+        if not 1 <= streams <= 8:
+            raise ValueError("streams must lie in 1 .. 8")
+        return RatizenConfig(int(raw["vocab"]), int(raw["width"]), float((raw.get("norm") or {}).get("eps", 1e-6)),
+                             float((raw.get("embedding") or {}).get("scale", 1.0)), float(raw.get("residual_mult", 1.0)), streams,
+                             "streams" in raw, float(raw.get("logit_scale", 1.0)), tuple(layers))
+
+
 # config.json "architecture" -> (config class, "module:class" of the model that lowers it to op lists)
 SEQUENCE_ARCHITECTURES = {
     "Sidalorn": (SidalornConfig, "sidalorn:SidalornModel"),
     "Redodra": (RedodraConfig, "redodra:RedodraModel"),
+    "Ratizen": (RatizenConfig, "ratizen:RatizenModel"),
 }
 
 

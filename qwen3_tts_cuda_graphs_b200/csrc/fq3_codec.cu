@@ -1048,6 +1048,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
   switch (o.kind) {
     case FQ3C_EMBED:
       if (!o.A || !o.B || !o.C) return fail("embed: missing operand");
+      if (o.i0 > 1 && o.K < o.N) return fail("embed: copies need a stride of at least N elements");
       if (o.flags & FQ3C_F32) fq3s_embed_kernel<float><<<o.M, 128, 0, s>>>(o);
       else fq3s_embed_kernel<bf16><<<o.M, 128, 0, s>>>(o);
       return 0;
@@ -1115,7 +1116,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       return 0;
     }
     case FQ3C_MOE_COMBINE:
-      if (!o.A || !o.B || !o.p0 || !o.p1 || !o.ws || !o.C) return fail("moe_combine: missing operand");
+      if (!o.A || !o.B || !o.p0 || !o.ws || !o.C) return fail("moe_combine: missing operand");
       fq3s_moe_combine_kernel<<<o.M, 256, 0, s>>>(o);
       return 0;
     case FQ3C_COMMIT:
@@ -1123,6 +1124,9 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       return 0;
     case FQ3C_LATENT_ATTN: {
       if (o.i0 < 1 || o.i1 < 1 || !o.A || !o.B || !o.C) return fail("latent_attn: missing operand");
+      if (o.cin < 0 || (o.cin > 0 && (!o.p1 || o.taps < o.i0 * o.cin)) || o.a_rows < 0 || (o.res && o.m_begin < o.i0))
+        return fail("latent_attn: bad score-only part, window or gate");
+      const int Dk = o.i1 + o.cin;      // a cache row: latent columns, then the score-only ones
       const int splits = std::max(1, o.K);
       if (splits > 64) return fail("latent_attn: at most 64 key splits");
       if (splits > 1 && (!o.ws || o.ws_bytes < (int64_t)o.M * o.i0 * splits * (o.i1 + 2) * 4)) return fail("latent_attn: workspace too small for the splits");
@@ -1130,16 +1134,16 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       static int use_mma = -1;
       if (use_mma < 0) { const char* e6 = getenv("FQ3S_ATTN_MMA"); use_mma = (e6 == nullptr || atoi(e6) != 0) ? 1 : 0; }
       const int RS = (o.i1 + 255) / 256;
-      if (use_mma && !(o.flags & FQ3C_F32) && RS <= 2 && o.i1 % 16 == 0 && o.i1 % (8 * RS) == 0 && o.ldr % 8 == 0 &&
+      if (use_mma && !(o.flags & FQ3C_F32) && RS <= 2 && o.i1 % 16 == 0 && o.i1 % (8 * RS) == 0 && o.cin % 16 == 0 && o.ldr % 8 == 0 &&
           !(reinterpret_cast<uintptr_t>(o.B) & 15)) {
-        const int TJ = o.i1 > 256 ? 32 : 64;
+        const int TJ = Dk > 256 ? 32 : 64;
         // one query (decoding): a block per split with all its warps on that query, R cut into up to eight 16-column-aligned slices
         int QB = LM_QB, RSk = RS;
         if (o.M == 1) {
           QB = 1;
           while (RSk < 8 && o.i1 % (32 * RSk) == 0) RSk *= 2;
         }
-        const size_t smem = (size_t)(QB * 16 + 2 * TJ) * (o.i1 + 8) * 2;   // queries + two key tiles
+        const size_t smem = (size_t)(QB * 16 + 2 * TJ) * (Dk + 8) * 2;   // queries + two key tiles
         const int nt_o = (o.i1 / RSk) / 8;
         static bool mattr[64] = {};
         int dev = 0;
@@ -1162,8 +1166,8 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
         return 0;
       }
       int HG = std::max(1, std::min(o.i0, o.i2 > 0 ? o.i2 : o.i0));
-      while (HG > 1 && latent_attn_smem(HG, o.i1) > 160 * 1024) --HG;
-      const size_t smem = latent_attn_smem(HG, o.i1);
+      while (HG > 1 && latent_attn_smem(HG, o.i1, o.cin) > 160 * 1024) --HG;
+      const size_t smem = latent_attn_smem(HG, o.i1, o.cin);
       if (smem > 200 * 1024) return fail("latent_attn: latent rank too large for shared memory");
       static bool attr[64] = {};
       int dev = 0;
@@ -1196,7 +1200,8 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       fq3s_xielu_kernel<<<dim3((o.N + 255) / 256, o.M), 256, 0, s>>>(o);
       return 0;
     case FQ3C_ROT_APPEND:
-      if (!o.A || o.i0 < 0 || o.i1 < 0 || o.i2 < 1 || o.taps < 0 || (o.taps & 1) || o.taps > o.i2 || (o.taps > 0 && !o.B) || (o.i1 > 0 && (!o.C || !o.C2)))
+      if (!o.A || o.i0 < 0 || o.i1 < 0 || o.i2 < 1 || o.taps < 0 || (o.taps & 1) || o.taps > o.i2 || (o.taps > 0 && !o.B) ||
+          (o.i1 > 0 && (!o.C || (o.cin > 0 && !o.C2))))
         return fail("rot_append: bad configuration");
       if (o.flags & FQ3C_F32) fq3s_rot_append_kernel<float><<<o.M, 256, 0, s>>>(o);
       else fq3s_rot_append_kernel<bf16><<<o.M, 256, 0, s>>>(o);
@@ -1255,6 +1260,24 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       }
       return 0;
     }
+    case FQ3C_HYPER: {
+      if (o.i0 < 1 || o.i0 > HY_MAX || !o.A || (o.i0 > 1 && o.K < o.N) || (o.res && (!o.p0 || !o.p1)) || (o.C && !o.bias) || (!o.C && !o.res))
+        return fail("hyper: 1 to 8 streams; mixing and write weights with a sublayer output; read weights with an output");
+      if ((size_t)o.N * 4 > 200 * 1024) return fail("hyper: row too wide for shared memory");
+      static bool hattr[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !hattr[dev]) {
+        cudaFuncSetAttribute(fq3s_hyper_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        hattr[dev] = true;
+      }
+      fq3s_hyper_kernel<<<o.M, 256, (size_t)o.N * 4, s>>>(o);
+      return 0;
+    }
+    case FQ3C_GLU:
+      if (!o.A || !o.C || o.N < 1) return fail("glu: missing operand");
+      fq3s_glu_kernel<<<dim3((o.N + 255) / 256, o.M), 256, 0, s>>>(o);
+      return 0;
     case FQ3C_MSTATE_SCAN: {
       if (o.i0 < 1 || o.i1 < 1 || o.i0 % o.i1 || o.i2 < 1 || o.cin < 1 || !o.A || !o.res || !o.scale || !o.p0 || !o.C || !o.C2 || !o.ws)
         return fail("mstate_scan: bad configuration");
@@ -1287,7 +1310,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
 
 extern "C" {
 
-int fq3c_abi_version(void) { return 7; }
+int fq3c_abi_version(void) { return 8; }
 const char* fq3c_last_error(void) { return g_err.c_str(); }
 int64_t fq3c_launch_count(void) { return g_launches.load(); }
 

@@ -530,7 +530,12 @@ __global__ void fq3s_embed_kernel(const fq3c_op o) {
   const int id = reinterpret_cast<const int*>(o.A)[m];
   const TB* row = reinterpret_cast<const TB*>(o.B) + (size_t)id * o.N;
   float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc;
-  for (int i = threadIdx.x; i < o.N; i += blockDim.x) c[i] = ldf<TB>(row + i);
+  const float sc = o.f0 != 0.f ? o.f0 : 1.f;
+  const int copies = max(o.i0, 1);
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
+    const float v = ldf<TB>(row + i) * sc;
+    for (int s = 0; s < copies; ++s) c[(size_t)s * (size_t)o.K + i] = v;
+  }
 }
 
 // grid (ceil(N / 256), M + taps - 1): rows >= M write the next history
@@ -669,12 +674,16 @@ __device__ __forceinline__ void router_token(const fq3c_op& o, const int m, floa
   float* ch = rsm + (size_t)n * tpb + tx;    // choice scores
   const float* z = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
   const float* corr = reinterpret_cast<const float*>(o.bias);
-  float mx = -INFINITY;
-  for (int i = 0; i < n; ++i) mx = fmaxf(mx, z[i]);
-  float sum = 0.f;
-  for (int i = 0; i < n; ++i) { const float e = expf(z[i] - mx); s[i * tpb] = e; sum += e; }
-  const float inv = 1.f / sum;
-  for (int i = 0; i < n; ++i) { const float v = s[i * tpb] * inv; s[i * tpb] = v; ch[i * tpb] = v + (corr ? corr[i] : 0.f); }
+  if (o.flags & FQ3C_SIGMOID) {
+    for (int i = 0; i < n; ++i) { const float v = sigmoid_f(z[i]); s[i * tpb] = v; ch[i * tpb] = v + (corr ? corr[i] : 0.f); }
+  } else {
+    float mx = -INFINITY;
+    for (int i = 0; i < n; ++i) mx = fmaxf(mx, z[i]);
+    float sum = 0.f;
+    for (int i = 0; i < n; ++i) { const float e = expf(z[i] - mx); s[i * tpb] = e; sum += e; }
+    const float inv = 1.f / sum;
+    for (int i = 0; i < n; ++i) { const float v = s[i * tpb] * inv; s[i * tpb] = v; ch[i * tpb] = v + (corr ? corr[i] : 0.f); }
+  }
   const int G = o.i1, keep = o.i2, gsz = n / max(G, 1);
   if (G > 1 && keep < G) {
     unsigned long long kept = 0ull;
@@ -709,7 +718,7 @@ __device__ __forceinline__ void router_token(const fq3c_op& o, const int m, floa
     wt[k] = sv;
     wsum += sv;
   }
-  const float sc = o.f0 / (wsum + 1e-20f);
+  const float sc = (o.flags & FQ3C_RAW_WEIGHTS) ? o.f0 : o.f0 / (wsum + 1e-20f);
   for (int k = 0; k < o.i0; ++k) wt[k] *= sc;
 }
 // With ws / p0 / p1 set (a single token, at most 16 choices, K = experts that have tensors) the launch also does the grouping
@@ -786,7 +795,7 @@ __global__ void __launch_bounds__(1024) fq3s_moe_sort_kernel(const fq3c_op o) {
 __global__ void __launch_bounds__(256) fq3s_moe_combine_kernel(const fq3c_op o) {
   const int m = blockIdx.x, top = o.i0;
   const int* ids = reinterpret_cast<const int*>(o.p0) + (size_t)m * top;
-  const float* w = reinterpret_cast<const float*>(o.p1) + (size_t)m * top;
+  const float* w = o.p1 ? reinterpret_cast<const float*>(o.p1) + (size_t)m * top : nullptr;
   const int* pos = reinterpret_cast<const int*>(o.ws) + (size_t)m * top;
   const float* Y = reinterpret_cast<const float*>(o.A);
   const float* x = reinterpret_cast<const float*>(o.B) + (size_t)m * o.ldr;
@@ -796,7 +805,7 @@ __global__ void __launch_bounds__(256) fq3s_moe_combine_kernel(const fq3c_op o) 
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const float v = ids[j] >= o.i1 ? x[i] : Y[(size_t)pos[j] * o.lda + i];
-      acc = fmaf(w[j], v, acc);
+      acc = w ? fmaf(w[j], v, acc) : acc + v;
     }
     if (sh) acc += sh[i];
     c[i] = acc;
@@ -820,46 +829,52 @@ __global__ void __launch_bounds__(256) fq3s_commit_kernel(const long long* desc,
 // included), several leave (max, sum, out) per split in ws and fq3s_latent_merge_kernel finishes.
 // ---------------------------------------------------------------------------------------------------------------------------
 constexpr int LA_TJ = 32;
-__host__ __device__ inline size_t latent_attn_smem(int HG, int R) {
-  return sizeof(float) * ((size_t)HG * R * 2 + (size_t)LA_TJ * (R + 1) + (size_t)HG * LA_TJ + 3 * (size_t)HG);
+__host__ __device__ inline size_t latent_attn_smem(int HG, int R, int E) {
+  return sizeof(float) * ((size_t)HG * (2 * R + E) + (size_t)LA_TJ * (R + E + 1) + (size_t)HG * LA_TJ + 3 * (size_t)HG);
 }
 template <typename TC>
 __global__ void __launch_bounds__(256) fq3s_latent_attn_kernel(const fq3c_op o, const int HG, const int splits) {
   extern __shared__ float lsm[];
-  const int R = o.i1, H = o.i0, m = blockIdx.x, h0 = blockIdx.y * HG, z = blockIdx.z;
+  // E more columns behind the R latent ones (a rotated key part) enter the scores only; D = R + E is a cache row's width
+  const int R = o.i1, E = o.cin, D = R + E, H = o.i0, m = blockIdx.x, h0 = blockIdx.y * HG, z = blockIdx.z;
   const int hg = min(HG, H - h0);
   float* qs = lsm;
-  float* os = qs + (size_t)HG * R;
+  float* os = qs + (size_t)HG * D;
   float* tile = os + (size_t)HG * R;
-  float* sc = tile + (size_t)LA_TJ * (R + 1);
+  float* sc = tile + (size_t)LA_TJ * (D + 1);
   float* mx = sc + (size_t)HG * LA_TJ;
   float* ls = mx + HG;
   float* al = ls + HG;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
-  const int nkeys = P + m + 1;
-  int per = (nkeys + splits - 1) / splits;
+  const int nkeys = P + m + 1, jbeg = o.a_rows > 0 ? max(0, nkeys - o.a_rows) : 0;      // a window's first key
+  int per = (nkeys - jbeg + splits - 1) / splits;
   per = (per + LA_TJ - 1) / LA_TJ * LA_TJ;
-  const int j0 = z * per, j1 = min(nkeys, j0 + per);
+  const int j0 = jbeg + z * per, j1 = min(nkeys, j0 + per);
   const float* q = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda + (size_t)h0 * R;
-  for (int i = tid; i < hg * R; i += blockDim.x) { qs[i] = q[i] * o.f0; os[i] = 0.f; }
+  const float* qe = E > 0 ? reinterpret_cast<const float*>(o.p1) + (size_t)m * o.taps + (size_t)h0 * E : nullptr;
+  for (int i = tid; i < hg * D; i += blockDim.x) {
+    const int h = i / D, r = i - h * D;
+    qs[i] = (r < R ? q[(size_t)h * R + r] : qe[(size_t)h * E + r - R]) * o.f0;
+  }
+  for (int i = tid; i < hg * R; i += blockDim.x) os[i] = 0.f;
   for (int i = tid; i < hg; i += blockDim.x) { mx[i] = -INFINITY; ls[i] = 0.f; }
   const TC* cache = reinterpret_cast<const TC*>(o.B);
   __syncthreads();
   for (int jt = j0; jt < j1; jt += LA_TJ) {
-    for (int i = tid; i < LA_TJ * R; i += blockDim.x) {
-      const int j = i / R, r = i - j * R;
-      tile[j * (R + 1) + r] = (jt + j < j1) ? ldf<TC>(cache + (size_t)(jt + j) * o.ldr + r) : 0.f;
+    for (int i = tid; i < LA_TJ * D; i += blockDim.x) {
+      const int j = i / D, r = i - j * D;
+      tile[j * (D + 1) + r] = (jt + j < j1) ? ldf<TC>(cache + (size_t)(jt + j) * o.ldr + r) : 0.f;
     }
     __syncthreads();
     for (int i = tid; i < hg * LA_TJ; i += blockDim.x) {
       const int h = i / LA_TJ, j = i - h * LA_TJ;
-      const float* qq = qs + (size_t)h * R;
-      const float* tt = tile + (size_t)j * (R + 1);
+      const float* qq = qs + (size_t)h * D;
+      const float* tt = tile + (size_t)j * (D + 1);
       float d0 = 0.f, d1 = 0.f;
       int r = 0;
-      for (; r + 1 < R; r += 2) { d0 = fmaf(qq[r], tt[r], d0); d1 = fmaf(qq[r + 1], tt[r + 1], d1); }
-      if (r < R) d0 = fmaf(qq[r], tt[r], d0);
+      for (; r + 1 < D; r += 2) { d0 = fmaf(qq[r], tt[r], d0); d1 = fmaf(qq[r + 1], tt[r + 1], d1); }
+      if (r < D) d0 = fmaf(qq[r], tt[r], d0);
       sc[i] = (jt + j < j1) ? d0 + d1 : -INFINITY;
     }
     __syncthreads();
@@ -881,13 +896,14 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_kernel(const fq3c_op o, 
       float acc = os[i] * al[h];
       const float* pp = sc + h * LA_TJ;
 #pragma unroll 8
-      for (int j = 0; j < LA_TJ; ++j) acc = fmaf(pp[j], tile[j * (R + 1) + r], acc);
+      for (int j = 0; j < LA_TJ; ++j) acc = fmaf(pp[j], tile[j * (D + 1) + r], acc);
       os[i] = acc;
     }
     __syncthreads();
   }
   if (splits == 1) {
     const float* sink = reinterpret_cast<const float*>(o.scale);
+    const float* gate = o.res ? reinterpret_cast<const float*>(o.res) + (size_t)m * o.m_begin + h0 : nullptr;
     float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h0 * R;
     for (int i = tid; i < hg * R; i += blockDim.x) {
       const int h = i / R;
@@ -897,6 +913,7 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_kernel(const fq3c_op o, 
         f = expf(mx[h] - mm);
         den = ls[h] * f + expf(sk - mm);
       }
+      if (gate) f *= sigmoid_f(gate[h]);
       c[i] = os[i] * f / den;
     }
   } else {
@@ -936,6 +953,7 @@ __global__ void __launch_bounds__(128) fq3s_latent_merge_kernel(const fq3c_op o,
   if (lane == 0) red[4 + warp] = den;
   __syncthreads();
   den = red[4] + red[5] + red[6] + red[7] + (sink ? expf(sk - mm) : 0.f);
+  if (o.res) den /= sigmoid_f(reinterpret_cast<const float*>(o.res)[(size_t)m * o.m_begin + h]);      // the head's output gate
   float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h * R;
   for (int r = tid; r < R; r += blockDim.x) {
     float acc = 0.f;
@@ -974,7 +992,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int NTM>
 __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op o, const int RS, const int splits, const int TJ, const int QB) {
   extern __shared__ __align__(16) unsigned char lm_raw[];
-  const int R = o.i1, H = o.i0, LDQ = R + 8;
+  const int R = o.i1, E = o.cin, D = R + E, H = o.i0, LDQ = D + 8;      // E score-only columns behind the R latent ones
   bf16* Qs = reinterpret_cast<bf16*>(lm_raw);          // [QB][16][LDQ]
   bf16* Ct0 = Qs + (size_t)QB * 16 * LDQ;           // two tiles [TJ][LDQ]: one is read while the next one arrives (cp.async)
   const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -982,18 +1000,23 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
   // the last queries see the most keys: their blocks start first
   const int m0 = (gridDim.x - 1 - blockIdx.x) * QB, h0 = blockIdx.y * 16, z = blockIdx.z;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
-  const int nk_max = P + min(o.M, m0 + QB);
-  int per = (nk_max + splits - 1) / splits;
+  const int nk_max = P + min(o.M, m0 + QB), W = o.a_rows;
+  const int jbeg = W > 0 ? max(0, P + m0 + 1 - W) : 0;      // the first key of the block's first (widest-reaching) window
+  int per = (nk_max - jbeg + splits - 1) / splits;
   per = (per + TJ - 1) / TJ * TJ;
-  const int j0 = z * per, j1 = min(nk_max, j0 + per);
+  const int j0 = jbeg + z * per, j1 = min(nk_max, j0 + per);
   const int m = m0 + wq;
   const bool active = m < o.M;
   const int nk = min(P + m + 1, j1);                   // this query's keys end here (inside this split)
+  const int klo = W > 0 ? P + m + 1 - W : 0;           // ... and begin here
   const float* A = reinterpret_cast<const float*>(o.A);
+  const float* A2 = reinterpret_cast<const float*>(o.p1);
   const int nq = min(QB, o.M - m0);                 // live queries of this block: the others' warps never read their rows
-  for (int i = tid; i < nq * 16 * R; i += nth) {
-    const int q = i / (16 * R), rem = i - q * 16 * R, h = rem / R, r = rem - h * R;
-    const float v = h0 + h < H ? A[(size_t)(m0 + q) * o.lda + (size_t)(h0 + h) * R + r] * o.f0 : 0.f;
+  for (int i = tid; i < nq * 16 * D; i += nth) {
+    const int q = i / (16 * D), rem = i - q * 16 * D, h = rem / D, r = rem - h * D;
+    float v = 0.f;
+    if (h0 + h < H)
+      v = (r < R ? A[(size_t)(m0 + q) * o.lda + (size_t)(h0 + h) * R + r] : A2[(size_t)(m0 + q) * o.taps + (size_t)(h0 + h) * E + r - R]) * o.f0;
     Qs[(q * 16 + h) * LDQ + r] = __float2bfloat16_rn(v);
   }
   float oacc[NTM][4];
@@ -1002,7 +1025,7 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
   const int cw = R / RS, nt_o = cw >> 3, c0 = wr * cw;
   const bf16* cache = reinterpret_cast<const bf16*>(o.B);
-  const int chunks = R >> 3;
+  const int chunks = D >> 3;
   const bf16* Qw = Qs + (size_t)wq * 16 * LDQ;
   auto fetch_tile = [&](const int jt, bf16* dst) {       // rows beyond the range arrive as zeros
     for (int i = tid; i < TJ * chunks; i += nth) {
@@ -1023,7 +1046,7 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (active && jt < nk) {
+    if (active && jt < nk && jt + TJ > klo) {
       float s[8][4];
 #pragma unroll
       for (int i = 0; i < 8; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
@@ -1033,7 +1056,7 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
         // B = two key octets x 16 columns of the tile (matrices: octet nt at kk, kk + 8, octet nt + 1 at kk, kk + 8)
         const bf16* qa = Qw + (size_t)((mi & 1) * 8 + l7) * LDQ + (mi >> 1) * 8;
         const bf16* cb = Ct + (size_t)((mi >> 1) * 8 + l7) * LDQ + (mi & 1) * 8;
-        for (int kk = 0; kk < R; kk += 16) {
+        for (int kk = 0; kk < D; kk += 16) {
           uint32_t a[4];
           ldmatrix_x4(a, qa + kk);
 #pragma unroll
@@ -1051,7 +1074,7 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int key = jt + nt * 8 + t * 2;
-        const bool v0 = (nt * 8 < TJ) && key < nk, v1 = (nt * 8 < TJ) && key + 1 < nk;
+        const bool v0 = (nt * 8 < TJ) && key < nk && key >= klo, v1 = (nt * 8 < TJ) && key + 1 < nk && key + 1 >= klo;
         if (!v0) { s[nt][0] = -INFINITY; s[nt][2] = -INFINITY; }
         if (!v1) { s[nt][1] = -INFINITY; s[nt][3] = -INFINITY; }
         mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
@@ -1129,7 +1152,8 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
         f = mr == -INFINITY ? 0.f : expf(mr - mm);
         den = lr * f + expf(sink[h] - mm);
       }
-      const float sc = f / den;
+      float sc = f / den;
+      if (o.res) sc *= sigmoid_f(reinterpret_cast<const float*>(o.res)[(size_t)m * o.m_begin + h]);
       float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h * R + c0;
 #pragma unroll
       for (int nt = 0; nt < NTM; ++nt)
@@ -1195,41 +1219,51 @@ __global__ void __launch_bounds__(256) fq3s_xielu_kernel(const fq3c_op o) {
   else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(v);
 }
 
-// grid (M), 256 threads.  Angles in f32: position (exact as a float below 2^24) times the frequency, full-range sincosf.
+// grid (M), 256 threads, a warp per query / key head.  Angles in f32: position (exact as a float below 2^24) times the frequency,
+// full-range sincosf; cos and sin times the amplitude f1 when that is set.  With norm weights a head is first divided by its root
+// mean square (eps f0) and multiplied by them.  Queries in place, keys (read from `res` rows when given) into the cache.
 template <typename TC>
 __global__ void __launch_bounds__(256) fq3s_rot_append_kernel(const fq3c_op o) {
   const int m = blockIdx.x, H = o.i0, G = o.i1, d = o.i2, dv = o.cin, half = o.taps >> 1;
   const int pos = (o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0) + m;
   float* row = const_cast<float*>(reinterpret_cast<const float*>(o.A)) + (size_t)m * o.lda;
+  const float* krow = o.res ? reinterpret_cast<const float*>(o.res) + (size_t)m * o.norm_ld : row;
   const float* freq = reinterpret_cast<const float*>(o.B);
-  const float fp = (float)pos;
-  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    float sn, cs;
-    sincosf(fp * freq[i], &sn, &cs);
-    float* e = row + (size_t)h * d + 2 * i;
-    const float a = e[0], b = e[1];
-    e[0] = a * cs - b * sn;
-    e[1] = b * cs + a * sn;
+  const float fp = (float)pos, amp = o.f1 != 0.f ? o.f1 : 1.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  TC* kc = G > 0 ? reinterpret_cast<TC*>(o.C) + (size_t)pos * o.ldc : nullptr;
+  for (int hh = warp; hh < H + G; hh += nwarp) {
+    const bool isq = hh < H;
+    const float* src = isq ? row + (size_t)hh * d : krow + o.K + (size_t)(hh - H) * d;
+    const float* nw = reinterpret_cast<const float*>(isq ? o.scale : o.bias);
+    float rs = 1.f;
+    if (nw) {
+      float ss = 0.f;
+      for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
+      rs = 1.f / sqrtf(warp_sum(ss) / (float)d + o.f0);
+    }
+    float* qd = isq ? row + (size_t)hh * d : nullptr;
+    TC* kd = isq ? nullptr : kc + (size_t)(hh - H) * d;
+    for (int i = lane; i < half; i += 32) {
+      float sn, cs;
+      sincosf(fp * freq[i], &sn, &cs);
+      sn *= amp; cs *= amp;
+      float a = src[2 * i], b = src[2 * i + 1];
+      if (nw) { a = a * rs * nw[2 * i]; b = b * rs * nw[2 * i + 1]; }
+      const float x = a * cs - b * sn, y = b * cs + a * sn;
+      if (isq) { qd[2 * i] = x; qd[2 * i + 1] = y; }
+      else { stf(kd + 2 * i, x); stf(kd + 2 * i + 1, y); }
+    }
+    if (isq && !nw) continue;     // the rest of a query head stays as it is
+    for (int c = 2 * half + lane; c < d; c += 32) {
+      const float v = nw ? src[c] * rs * nw[c] : src[c];
+      if (isq) qd[c] = v;
+      else stf(kd + c, v);
+    }
   }
-  if (G <= 0) return;
-  TC* kc = reinterpret_cast<TC*>(o.C) + (size_t)pos * o.ldc;
+  if (G <= 0 || dv <= 0) return;
   TC* vc = reinterpret_cast<TC*>(o.C2) + (size_t)pos * o.ldr;
-  const float* k = row + o.K;
-  const float* v = row + o.a_rows;
-  for (int idx = threadIdx.x; idx < G * half; idx += blockDim.x) {
-    const int g = idx / half, i = idx - g * half;
-    float sn, cs;
-    sincosf(fp * freq[i], &sn, &cs);
-    const float a = k[(size_t)g * d + 2 * i], b = k[(size_t)g * d + 2 * i + 1];
-    stf(kc + (size_t)g * d + 2 * i, a * cs - b * sn);
-    stf(kc + (size_t)g * d + 2 * i + 1, b * cs + a * sn);
-  }
-  const int rest = d - 2 * half;
-  for (int idx = threadIdx.x; idx < G * rest; idx += blockDim.x) {
-    const int g = idx / rest, c = 2 * half + idx - g * rest;
-    stf(kc + (size_t)g * d + c, k[(size_t)g * d + c]);
-  }
+  const float* v = krow + o.a_rows;
   for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x) stf(vc + idx, v[idx]);
 }
 
@@ -1245,8 +1279,15 @@ __host__ __device__ inline size_t cache_attn_smem(int R, int TJ, int d, int dv) 
   return sizeof(float) * ((size_t)R * d + (size_t)TJ * (d + 1) + (size_t)TJ * dv + (size_t)R * TJ + (size_t)R * dv + 3 * (size_t)R);
 }
 struct CacheAttnMask {
-  int window, keep;
-  __device__ __forceinline__ bool sees(int i, int j) const { return j <= i && (window <= 0 || i - j < window || j < keep); }
+  int window, keep, chunk;
+  __device__ __forceinline__ bool sees(int i, int j) const {
+    return j <= i && (window <= 0 || i - j < window || j < keep) && (chunk <= 0 || j >= i - i % chunk);
+  }
+  // no query at position >= i sees a key below this
+  __device__ __forceinline__ int lowest(int i) const {
+    const int wlo = (window > 0 && keep <= 0) ? max(0, i - window + 1) : 0;
+    return max(wlo, chunk > 0 ? i - i % chunk : 0);
+  }
 };
 // rows [0, nvalid) of a cache tile into shared memory as f32 (the rest of the nrows as zeros): 16-byte loads, several in flight,
 // where the rows allow them
@@ -1299,11 +1340,12 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_kernel(const fq3c_op o, c
   float* al = ls + R;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
-  const CacheAttnMask mask{o.K, o.a_rows};
+  const CacheAttnMask mask{o.K, o.a_rows, o.tap_off[0]};
   const int ifirst = P + m0, ilast = P + m0 + nq - 1;
-  const int ntiles = ilast / TJ + 1;
-  const int per = (ntiles + splits - 1) / splits;
-  const int t0 = z * per, t1 = min(ntiles, t0 + per);
+  // the splits share the tiles from the first one any query of the block can see
+  const int ntiles = ilast / TJ + 1, tbeg = mask.lowest(ifirst) / TJ;
+  const int per = (ntiles - tbeg + splits - 1) / splits;
+  const int t0 = tbeg + z * per, t1 = min(ntiles, t0 + per);
   for (int idx = tid; idx < R * d; idx += blockDim.x) {
     const int r = idx / d, c = idx - r * d, qi = r / HG, hh = r - qi * HG;
     qs[idx] = qi < nq ? reinterpret_cast<const float*>(o.A)[(size_t)(m0 + qi) * o.lda + (size_t)(g * HG + hh) * d + c] : 0.f;
@@ -1318,6 +1360,7 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_kernel(const fq3c_op o, c
     const int j0 = t * TJ, jn = min(TJ, ilast + 1 - j0);
     // nothing of this tile is inside the widest window of the block (that of its first query) nor among the kept positions
     if (mask.window > 0 && j0 + jn <= ifirst - mask.window + 1 && j0 >= mask.keep) continue;
+    if (mask.chunk > 0 && j0 + jn <= ifirst - ifirst % mask.chunk) continue;
     __syncthreads();
     ca_stage_rows<TC>(kt, d + 1, kc + (size_t)j0 * o.ldr, o.ldr, jn, TJ, d, tid, blockDim.x);
     ca_stage_rows<TC>(vt, dv, vc + (size_t)j0 * o.taps, o.taps, jn, TJ, dv, tid, blockDim.x);
@@ -1453,7 +1496,7 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
   const int m0 = (gridDim.x - 1 - blockIdx.x) * QBLK, kvh = blockIdx.y;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
   const int nq = min(QBLK, o.M - m0), ifirst = P + m0, ilast = ifirst + nq - 1;
-  const int W = o.K, keep = o.a_rows;
+  const int W = o.K, keep = o.a_rows, chunk = o.tap_off[0];
   const float* A = reinterpret_cast<const float*>(o.A);
   if (o.lda % 4 == 0 && !(reinterpret_cast<uintptr_t>(A) & 15)) {      // 16-byte loads, four in flight per thread
     const int c4 = d >> 2;
@@ -1473,20 +1516,22 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
     }
   }
   // the two rows this thread holds of its warp's 16
-  int qpos[2], head[2];
+  int qpos[2], head[2], clo[2];
   bool live[2];
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int r = warp * 16 + g + e * 8, qi = r / HG;
     live[e] = qi < nq;
     qpos[e] = ifirst + qi;
+    clo[e] = chunk > 0 ? qpos[e] - qpos[e] % chunk : 0;      // first key of the query's chunk
     head[e] = kvh * HG + (r - qi * HG);
   }
   const bool wactive = (warp * 16) / HG < nq;
   const int wfirst = ifirst + (warp * 16) / HG, wlast = ifirst + min(nq - 1, (warp * 16 + 15) / HG);
   const int ntiles = ilast / CM_TJ + 1;
   const int tkeep = W > 0 ? (keep + CM_TJ - 1) / CM_TJ : 0, tlo = W > 0 ? max(0, ifirst - W + 1) / CM_TJ : 0;
-  auto next_tile = [&](int tt) { ++tt; if (W > 0 && tt >= tkeep && tt < tlo) tt = tlo; return tt; };
+  const int tstart = chunk > 0 ? (ifirst - ifirst % chunk) / CM_TJ : 0;      // tiles below the first query's chunk: nobody sees them
+  auto next_tile = [&](int tt) { ++tt; if (tt < tstart) tt = tstart; if (W > 0 && tt >= tkeep && tt < tlo) tt = tlo; return tt; };
   const bf16* kc = reinterpret_cast<const bf16*>(o.B) + (size_t)kvh * d;
   const bf16* vc = reinterpret_cast<const bf16*>(o.p1) + (size_t)kvh * dv;
   const int kch = d >> 3, vch = dv >> 3;
@@ -1551,7 +1596,7 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
         }
       }
       // a tile every row of the warp sees whole needs no per-score test (most tiles of a long portion)
-      const bool whole = nq == QBLK && jt + CM_TJ - 1 <= wfirst && (W <= 0 || wlast - jt < W);
+      const bool whole = nq == QBLK && jt + CM_TJ - 1 <= wfirst && (W <= 0 || wlast - jt < W) && (chunk <= 0 || jt >= wlast - wlast % chunk);
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
@@ -1559,7 +1604,7 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
         for (int e = 0; e < 4; ++e) {
           const int key = jt + nt * 8 + t * 2 + (e & 1), hf = e >> 1, i = qpos[hf];
           float v = -INFINITY;
-          if (whole || (live[hf] && key <= i && (W <= 0 || i - key < W || key < keep))) {
+          if (whole || (live[hf] && key <= i && key >= clo[hf] && (W <= 0 || i - key < W || key < keep))) {
             v = s[nt][e] * o.f0;
             if (cap > 0.f) v = cap * fast_tanh(v * icap);
             if (r12) v -= r1v[hf] * __logf(fmaf(r2v[hf], (float)(i - key), 1.f));
@@ -1847,4 +1892,75 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   float* nst = reinterpret_cast<float*>(o.C2) + (size_t)h * dk * dv;
 #pragma unroll
   for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; if (live && i < dk) nst[(size_t)i * dv + col] = S[r]; }
+}
+
+// ===========================================================================================================================
+// ABI 8 (kinds 30-31): several residual streams with learned read / write / mixing weights, and the gated unit of routed experts
+// whose weight multiplies the expert's input.
+// ===========================================================================================================================
+constexpr int HY_MAX = 8;
+// grid (M), 256 threads, dynamic shared memory N floats (the row's read-out u).  One pass writes the streams back (when a
+// sublayer's output is given) and forms u; a second one norms it.  Everything f32.
+__global__ void __launch_bounds__(256) fq3s_hyper_kernel(const fq3c_op o) {
+  extern __shared__ float hsm[];
+  __shared__ float red[32];
+  const int m = blockIdx.x, S = o.i0;
+  float* X = const_cast<float*>(reinterpret_cast<const float*>(o.A)) + (size_t)m * o.lda;
+  const float* y = o.res ? reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr : nullptr;
+  const float* mix = reinterpret_cast<const float*>(o.p0);
+  const float* wo = reinterpret_cast<const float*>(o.p1);
+  const float* wi = reinterpret_cast<const float*>(o.bias);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < o.N; c += blockDim.x) {
+    float xs[HY_MAX], xn[HY_MAX];
+#pragma unroll
+    for (int s = 0; s < HY_MAX; ++s) xs[s] = s < S ? X[(size_t)s * (size_t)o.K + c] : 0.f;
+    if (y) {
+      const float yv = o.f1 * y[c];
+#pragma unroll
+      for (int t = 0; t < HY_MAX; ++t) {
+        if (t >= S) continue;
+        float acc = wo[t] * yv;
+#pragma unroll
+        for (int s = 0; s < HY_MAX; ++s)
+          if (s < S) acc = fmaf(mix[s * S + t], xs[s], acc);
+        xn[t] = acc;
+        X[(size_t)t * (size_t)o.K + c] = acc;
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < HY_MAX; ++t) xn[t] = xs[t];
+    }
+    if (o.C) {
+      float u = 0.f;
+#pragma unroll
+      for (int t = 0; t < HY_MAX; ++t)
+        if (t < S) u = fmaf(wi[t], xn[t], u);
+      hsm[c] = u;
+      ss = fmaf(u, u, ss);
+    }
+  }
+  if (!o.C) return;
+  const float* w = reinterpret_cast<const float*>(o.scale);
+  float rs = 1.f;
+  if (w) rs = 1.f / sqrtf(seq_block_sum(ss, red) / (float)o.N + o.f0);
+  for (int c = threadIdx.x; c < o.N; c += blockDim.x) {      // a thread reads back what it wrote itself
+    const float v = w ? hsm[c] * rs * w[c] : hsm[c];
+    if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + c] = v;
+    else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(v);
+  }
+}
+
+// grid (ceil(N / 256), M)
+__global__ void __launch_bounds__(256) fq3s_glu_kernel(const fq3c_op o) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, q = blockIdx.y;
+  if (c >= o.N) return;
+  const int r = o.ws ? reinterpret_cast<const int*>(o.ws)[q] : q;
+  if (r < 0) return;
+  const float w = o.p1 ? reinterpret_cast<const float*>(o.p1)[q] : 1.f;
+  const float* a = reinterpret_cast<const float*>(o.A) + (size_t)r * o.lda;
+  const float g = w * a[c], u = w * a[o.N + c];
+  const float v = g / (1.f + expf(-g)) * u;
+  if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)r * o.ldc + c] = v;
+  else reinterpret_cast<bf16*>(o.C)[(size_t)r * o.ldc + c] = __float2bfloat16_rn(v);
 }

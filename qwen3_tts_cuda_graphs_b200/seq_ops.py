@@ -4,13 +4,16 @@ A `StepBuilder` lowers ONE step (M new tokens of the request in one slot) to a f
 it allocates; the list is handed to `fq3c_run` / replayed as a CUDA graph like the codec's plans.  Each mechanism is a method
 with its constants as arguments, so another design composes them differently:
 
-  embed, time_conv (causal per-channel convolution with carried inputs), group_norm (RMS norm in groups, optional residual
-  add, optional silu gate before or after), dyt (dynamic-tanh norm, optionally chained into the next one), depth_mix (weighted
+  embed (optionally scaled and copied into several residual streams), hyper (several residual streams: write a sublayer's
+  output back through mixing / write weights, read the next sublayer's normed input), time_conv (causal per-channel convolution
+  with carried inputs), group_norm (RMS norm in groups, optional residual add, optional silu gate before or after), dyt (dynamic-tanh norm, optionally chained into the next one), depth_mix (weighted
   sum over the outputs of all layers so far), linear (tcgen05 GEMM, or the CUDA-core / GEMV product for true 32-bit, decode
-  rows and odd shapes), latent_attention (low-rank shared latent cache, absorbed projections, sink softmax), softmax_attention
-  (key / value cache, grouped heads, partial rotary, score cap, window with kept first positions, distance penalty, sink,
-  output gate, borrowed cache), rglru (gated diagonal linear recurrence block), delta_rule and state_space (matrix state per
-  head), polynorm_ff, xielu_ff, moe_ff (softmax router with correction, neighbour groups, identity experts, shared expert).
+  rows and odd shapes), latent_attention (low-rank shared latent cache, absorbed projections, sink softmax; optionally a query
+  latent, a rotary key part shared by the heads with a scaled rotary table, a sliding window, an output gate), softmax_attention
+  (key / value cache, grouped heads, partial rotary, per-head query / key norms, score cap, window with kept first positions,
+  chunked mask, distance penalty, sink, output gate, borrowed cache), rglru (gated diagonal linear recurrence block), delta_rule and state_space (matrix state per
+  head), polynorm_ff, xielu_ff, moe_ff (softmax or sigmoid router with correction, neighbour groups, identity experts, shared
+  expert; gelu or gated experts; weights on the experts' outputs or inputs).
 
 Precision: `f32=True` runs every product in true 32-bit.  Otherwise weights and product operands are bf16 with f32
 accumulation; the residual stream, norms, softmax, router, recurrence and everything entering it are f32 in both modes.
@@ -21,9 +24,9 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .codec import (F_A_F32, F_BIAS, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RESID, F_SIGMOID, F_SILU, K_BDGEMM,
-                    K_CACHE_ATTN, K_COMMIT, K_DEPTH_MIX, K_DYT, K_EMBED, K_GEMM, K_GGEMM, K_GNORM, K_LATENT_ATTN, K_LRU_SCAN,
-                    K_MOE_COMBINE, K_MOE_SORT, K_MSTATE_SCAN, K_POLYNORM, K_ROT_APPEND, K_ROUTER, K_TCONV, K_XIELU, Op, _Plan)
+from .codec import (F_A_F32, F_BIAS, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RAW_WEIGHTS, F_RESID, F_SIGMOID, F_SILU,
+                    K_BDGEMM, K_CACHE_ATTN, K_COMMIT, K_DEPTH_MIX, K_DYT, K_EMBED, K_GEMM, K_GGEMM, K_GLU, K_GNORM, K_HYPER, K_LATENT_ATTN,
+                    K_LRU_SCAN, K_MOE_COMBINE, K_MOE_SORT, K_MSTATE_SCAN, K_POLYNORM, K_ROT_APPEND, K_ROUTER, K_TCONV, K_XIELU, Op, _Plan)
 from .config import DeltaRuleConfig, LatentAttentionConfig, MoEFFConfig, RglruConfig, SoftmaxAttentionConfig, StateSpaceConfig
 from .seq_state import SlotState
 
@@ -65,10 +68,35 @@ class StepBuilder:
         return F_OUT_F32 if out.dtype == torch.float32 else 0
 
     # ---- mechanisms -----------------------------------------------------------------------------
-    def embed(self, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
-        """out f32 [rows, N] = table[ids]; also a row gather from an f32 matrix (F_F32)."""
-        self._op(K_EMBED, M=rows or self.M, N=table.shape[1], A=ids, B=table, C=out, ldc=out.shape[1],
-                 flags=F_F32 if table.dtype == torch.float32 else 0)
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None, scale: float = 0.0,
+              copies: int = 1):
+        """out f32 [rows, N] = table[ids] (* scale); also a row gather from an f32 matrix (F_F32).  copies > 1: out is
+        [copies, rows, N] and every slice gets the rows (residual streams that start equal)."""
+        kw = {}
+        if copies > 1:
+            assert out.dim() == 3 and out.shape[0] == copies and out.is_contiguous()
+            kw = dict(i0=copies, K=out.shape[1] * out.shape[2])
+        self._op(K_EMBED, M=rows or self.M, N=table.shape[1], A=ids, B=table, C=out, ldc=out.shape[-1], f0=float(scale),
+                 flags=F_F32 if table.dtype == torch.float32 else 0, **kw)
+        return out
+
+    def hyper(self, X: torch.Tensor, out: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None,
+              norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, y: Optional[torch.Tensor] = None,
+              mix: Optional[torch.Tensor] = None, write: Optional[torch.Tensor] = None, mult: float = 1.0):
+        """Residual streams X f32 [S, M, N].  With y (a sublayer's output, f32 [M, N]): X_t <- sum_s mix[s, t] X_s + mult * write[t] * y.
+        Then, with out: u = sum_s read[s] X_s and out = u / rms(u) * norm_w (product-operand dtype or f32), or u itself when norm_w
+        is None (out f32).  One launch."""
+        S, M, N = X.shape
+        kw = dict(M=M, N=N, i0=S, K=M * N, A=X, lda=N, f0=float(eps), f1=float(mult))
+        if y is not None:
+            kw.update(res=y, ldr=y.shape[1], p0=mix, p1=write)
+        if out is not None:
+            kw.update(C=out, ldc=out.shape[1], bias=read, flags=self._oflag(out))
+            if norm_w is not None:
+                kw["scale"] = norm_w
+            else:
+                assert out.dtype == torch.float32
+        self._op(K_HYPER, **kw)
         return out
 
     def time_conv(self, x: torch.Tensor, w: torch.Tensor, state: str, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -143,21 +171,44 @@ class StepBuilder:
     def latent_attention(self, h: torch.Tensor, c: LatentAttentionConfig, w: dict, cache: str, eps: float, out: torch.Tensor):
         """h [M, width] (product-operand dtype) -> out f32 [M, width].  w: wqd [H*dim + rank, width], dkv_norm f32 [rank],
         uk_t [H, rank, dim] (the key up-projection per head, transposed: queries are carried into latent space), uv [H, vdim, rank],
-        sink f32 [H] or None, o [width, H*vdim]."""
-        M, H, R = self.M, c.heads, c.kv_rank
-        qd = self.linear(h, w["wqd"], self.buf("la.qd", M, H * c.dim + R))
+        sink f32 [H] or None, o [width, H*vdim].
+
+        With the options of LatentAttentionConfig (E = rot_dim): wqd = [Q | dkv (rank) | rotary key part (E) | gate rows (H)] where
+        Q is the query latent's down-projection (q_rank rows; then dq_norm f32 [q_rank] and uq [H*dim + H*E, q_rank]) or the query
+        projection itself, in both cases laid out as all heads' plain parts, then all heads' rotary parts; freq f32 [E / 2] and
+        amp (float): the rotary table.  A cache row is [latent (rank) | rotated key part (E)]."""
+        M, H, R, E = self.M, c.heads, c.kv_rank, c.rot_dim
+        nq = H * (c.dim + E)
+        qcols = c.q_rank if c.q_rank > 0 else nq
+        qd = self.linear(h, w["wqd"], self.buf("la.qd", M, w["wqd"].shape[0]))
         ctab = self.slot.cur[cache]
-        self.group_norm(qd, w["dkv_norm"], 1, eps, ctab, n=R, col=H * c.dim, append_at_position=True)
-        qa = self.block_linear(qd, w["uk_t"], self.buf("la.qa", M, H * R))
+        cf32 = F_F32 if ctab.dtype == torch.float32 else 0
+        self.group_norm(qd, w["dkv_norm"], 1, eps, ctab, n=R, col=qcols, append_at_position=True)
+        if c.q_rank > 0:
+            cq = self.group_norm(qd, w["dq_norm"], 1, eps, self.buf("la.cq", M, c.q_rank, self.adt), n=c.q_rank)
+            q, qcol = self.linear(cq, w["uq"], self.buf("la.q", M, nq)), 0
+        else:
+            q, qcol = qd, 0
+        if E > 0:   # rotary parts: the heads' query parts turn in place, the one key part goes into the cache behind the latent
+            self.plan.keep += [q, qd]
+            self._op(K_ROT_APPEND, M=M, i0=H, i1=1, i2=E, taps=E, cin=0, A=_ptr(q, qcol + H * c.dim), lda=q.shape[1], B=w["freq"],
+                     f1=float(w.get("amp", 1.0)), res=qd, norm_ld=qd.shape[1], K=qcols + R, C=_ptr(ctab, R), ldc=ctab.shape[1],
+                     p0=self.slot.pos, flags=cf32)
+        qa = self.block_linear(q, w["uk_t"], self.buf("la.qa", M, H * R), col=qcol)
         # key-range splits: a long step has blocks enough; a few rows (decoding) spread their keys over up to 64 blocks of one or
         # more 64-key tiles each, sized by what the slot can hold (the list is built once for every position)
         # (the tensor-core kernel runs 4 queries x 16 heads per block, the CUDA-core one a query per block; ~2 blocks per SM wanted)
-        tiles = max(1, -(-self.slot.max_pos // 64))
+        span = min(self.slot.max_pos, c.window) if c.window > 0 else self.slot.max_pos
+        tiles = max(1, -(-span // 64))
         blocks = M if ctab.dtype == torch.float32 else -(-M // 4) * -(-H // 16)
         splits = min(64, tiles) if M <= 8 else (1 if blocks >= 74 else max(1, min(16, tiles, -(-296 // blocks))))   # half the SMs busy: no split
         oa = self.buf("la.oa", M, H * R)
         kw = dict(M=M, N=H * R, K=splits, i0=H, i1=R, i2=H, f0=c.scale, A=qa, lda=qa.shape[1], B=ctab, ldr=ctab.shape[1], p0=self.slot.pos,
-                  C=oa, ldc=oa.shape[1], flags=F_F32 if ctab.dtype == torch.float32 else 0)
+                  C=oa, ldc=oa.shape[1], flags=cf32, a_rows=max(c.window, 0))
+        if E > 0:
+            kw.update(cin=E, p1=_ptr(q, qcol + H * c.dim), taps=q.shape[1])
+        if c.gate:
+            kw.update(res=_ptr(qd, qcols + R + E), m_begin=qd.shape[1])
         if w.get("sink") is not None:
             kw["scale"] = w["sink"]
         if splits > 1:
@@ -214,11 +265,12 @@ class StepBuilder:
         return out
 
     # ---- softmax attention over a key / value cache ---------------------------------------------------
-    def softmax_attention(self, h: torch.Tensor, c: SoftmaxAttentionConfig, w: dict, kcache: str, vcache: str, out: torch.Tensor):
+    def softmax_attention(self, h: torch.Tensor, c: SoftmaxAttentionConfig, w: dict, kcache: str, vcache: str, out: torch.Tensor,
+                          eps: float = 1e-6):
         """h [M, width] (product-operand dtype) -> out f32 [M, width].  w: wqkv [(H + 2G) dim.. (+ H gate rows), width] — queries, then
         (unless the layer borrows a cache) keys and values, then the gate rows; bqkv f32 or None; freq f32 [rot_dims / 2] or None;
-        sink f32 [H] or None; r12 f32 [2H] or None; o [width, H * vdim]; o_b f32 or None.  kcache / vcache name the slot's
-        append states to write (own projections) and read."""
+        sink f32 [H] or None; r12 f32 [2H] or None; o [width, H * vdim]; o_b f32 or None; q_norm / k_norm f32 [dim] with qk_norm
+        (eps: their epsilon).  kcache / vcache name the slot's append states to write (own projections) and read."""
         M, H, G, d, dv = self.M, c.heads, c.kv_heads, c.dim, c.vdim
         own = c.kv_from is None
         kcol = H * d
@@ -227,18 +279,25 @@ class StepBuilder:
         proj = self.linear(h, w["wqkv"], self.buf("sa.proj", M, w["wqkv"].shape[0]), bias=w.get("bqkv"))
         kc, vc = self.slot.cur[kcache], self.slot.cur[vcache]
         cf32 = F_F32 if kc.dtype == torch.float32 else 0
-        if own or c.rot_dims > 0:
+        if own or c.rot_dims > 0 or c.qk_norm:
             kw = dict(M=M, i0=H, i1=G if own else 0, i2=d, cin=dv, taps=c.rot_dims, K=kcol, a_rows=vcol, A=proj, lda=proj.shape[1],
                       p0=self.slot.pos, flags=cf32)
             if c.rot_dims > 0:
                 kw["B"] = w["freq"]
+            if c.qk_norm:   # per-head norms in the same launch, before the rotation
+                kw.update(scale=w["q_norm"], bias=w["k_norm"], f0=float(eps))
             if own:
                 kw.update(C=kc, ldc=kc.shape[1], C2=vc, ldr=vc.shape[1])
             self._op(K_ROT_APPEND, **kw)
         # key-range splits: many query blocks need none; a few rows (decoding) spread their keys over up to 64 blocks
         HG = H // G
         QB = 1 if M == 1 else max(1, min(16, M, 16 // HG))
-        tiles = max(1, -(-self.slot.max_pos // 32))
+        span = self.slot.max_pos        # the most keys a query can see
+        if c.window > 0 and c.keep_first == 0:
+            span = min(span, c.window)
+        if c.chunk > 0:
+            span = min(span, c.chunk)
+        tiles = max(1, -(-span // 32))
         blocks = -(-M // QB) * G
         splits = min(64, tiles) if M <= 8 else (1 if blocks >= 74 else max(1, min(16, tiles, -(-296 // blocks))))
         oa = self.buf("sa.o", M, H * dv, self.adt)
@@ -254,7 +313,8 @@ class StepBuilder:
         if splits > 1:
             ws = self.buf("sa.ws", 1, M * H * splits * (dv + 2))
             kw["ws"], kw["ws_bytes"] = ws, ws.numel() * 4
-        self._op(K_CACHE_ATTN, **kw)
+        op = self._op(K_CACHE_ATTN, **kw)
+        op.tap_off[0] = max(c.chunk, 0)
         return self.linear(oa, w["o"], out, bias=w.get("o_b"))
 
     # ---- recurrences with a matrix state per head -----------------------------------------------------
@@ -311,7 +371,9 @@ class StepBuilder:
 
     def moe_ff(self, x32: torch.Tensor, xop: torch.Tensor, c: MoEFFConfig, w: dict, out: torch.Tensor):
         """x32: the f32 rows (identity experts); xop: the same rows as product operands.  w: router [n, width], correction f32 [n]
-        or None, up [E, ff, width], down [E, width, ff], shared_up / shared_down or None.  The router's logits are f32 either way:
+        or None, up [E, ff, width], down [E, width, ff], shared_up / shared_down or None.  Gated experts (c.gated): up is
+        [E, 2 ff, width] and shared_up [2 shared_ff, width], gate rows first, then up rows; the unit is silu(gate) * up, and with
+        c.weight_input the choice's weight multiplies both (the expert's input) instead of the expert's output.  The router's logits are f32 either way:
         f32 router weights take the f32 rows (true 32-bit product); bf16 ones take the bf16 rows, whose products with the weights
         are exact in f32 and are summed in f32."""
         M, n, top, E = self.M, c.routed, c.top, c.experts
@@ -319,7 +381,8 @@ class StepBuilder:
         z = self.linear(x32 if w["router"].dtype == torch.float32 else xop, w["router"], self.buf("moe.z", M, n))
         ids = self.buf("moe.ids", M, top, torch.int32)
         wt = self.buf("moe.w", M, top)
-        kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=n, C=ids, C2=wt)
+        kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=n, C=ids, C2=wt,
+                  flags=(F_SIGMOID if c.score == "sigmoid" else 0) | (0 if c.renorm else F_RAW_WEIGHTS))
         if w.get("correction") is not None:
             kw["bias"] = w["correction"]
         seg = self.buf("moe.seg", 1, E + 1, torch.int32)
@@ -333,19 +396,45 @@ class StepBuilder:
         ff = c.expert_ff
         f32 = xop.dtype == torch.float32
         act = self.buf("moe.act", M * top, ff, self.adt)
-        self._op(K_GGEMM, M=M * top, N=ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=act, ldc=ff,
-                 flags=F_GELU | self._oflag(act) | (F_F32 if f32 else 0))
+        if c.gated:
+            gu = self.buf("moe.gu", M * top, 2 * ff)
+            self._op(K_GGEMM, M=M * top, N=2 * ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=gu, ldc=2 * ff,
+                     flags=F_OUT_F32 | (F_F32 if f32 else 0))
+            self.glu(gu, act, pairs=M * top, place=pos, weight=wt if c.weight_input else None)
+        else:
+            assert not c.weight_input
+            self._op(K_GGEMM, M=M * top, N=ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=act, ldc=ff,
+                     flags=F_GELU | self._oflag(act) | (F_F32 if f32 else 0))
         y = self.buf("moe.y", M * top, width)
         self._op(K_GGEMM, M=M * top, N=width, K=ff, i0=E, A=act, lda=ff, B=w["down"], p0=seg, C=y, ldc=width,
                  flags=F_OUT_F32 | (F_F32 if f32 else 0))
         sh = None
-        if w.get("shared_up") is not None:
+        if w.get("shared_up") is not None and c.gated:
+            sg = self.linear(xop, w["shared_up"], self.buf("moe.sg", M, w["shared_up"].shape[0]))
+            sa = self.glu(sg, self.buf("moe.sa", M, w["shared_up"].shape[0] // 2, self.adt))
+            sh = self.linear(sa, w["shared_down"], self.buf("moe.sh", M, width))
+        elif w.get("shared_up") is not None:
             sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0], self.adt), gelu=True)
             sh = self.linear(sa, w["shared_down"], self.buf("moe.sh", M, width))
-        kw = dict(M=M, N=width, i0=top, i1=E, A=y, lda=width, B=x32, ldr=width, p0=ids, p1=wt, ws=pos, C=out, ldc=out.shape[1])
+        kw = dict(M=M, N=width, i0=top, i1=E, A=y, lda=width, B=x32, ldr=width, p0=ids, ws=pos, C=out, ldc=out.shape[1])
+        if not c.weight_input:
+            kw["p1"] = wt
         if sh is not None:
             kw["res"] = sh
         self._op(K_MOE_COMBINE, **kw)
+        return out
+
+    def glu(self, gu: torch.Tensor, out: torch.Tensor, pairs: Optional[int] = None, place: Optional[torch.Tensor] = None,
+            weight: Optional[torch.Tensor] = None):
+        """out[r] = silu(w gate) * (w up) for rows gu f32 [.., 2 N] = [gate | up].  place (int32 [pairs]) / weight (f32 [pairs]): pair q
+        works on row place[q] (negative: none) with w = weight[q]; without them row q itself with w = 1."""
+        n = gu.shape[1] // 2
+        kw = dict(M=pairs or self.M, N=n, A=gu, lda=gu.shape[1], C=out, ldc=out.shape[1], flags=self._oflag(out))
+        if place is not None:
+            kw["ws"] = place
+        if weight is not None:
+            kw["p1"] = weight
+        self._op(K_GLU, **kw)
         return out
 
     def commit(self):
