@@ -56,9 +56,10 @@ def streams_write(X: torch.Tensor, mix: torch.Tensor, w_out: torch.Tensor, mult:
 
 
 # ---- attention over keys of the same chunk, with a valueless zero-score sink -------------------------------------------------
-def chunk_sink_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
+def chunk_sink_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float, sink: bool = True) -> torch.Tensor:
     """h [T, width].  Grouped heads, per-head RMS norm of queries and keys (one weight vector for all heads), no positions in the
-    scores; position i sees j <= i of its own chunk (i // size == j // size); p_j = e^{s_j} / (1 + sum_j e^{s_j})."""
+    scores; position i sees j <= i of its own chunk (i // size == j // size); p_j = e^{s_j} / (1 + sum_j e^{s_j}).
+    sink=False (not part of the design; tests use it to show that the one in the denominator matters): plain softmax."""
     T = h.shape[0]
     H, G, d, dv, size, scale = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"], m["scale"]
     q = (h @ W[p + "q"].T).reshape(T, H, d)
@@ -74,7 +75,7 @@ def chunk_sink_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m:
             s = (k[lo:i + 1, g] @ q[i, hh]) * scale
             mx = max(float(s.max()), 0.0)
             e = torch.exp(s - mx)
-            pr = e / (math.exp(-mx) + e.sum())
+            pr = e / ((math.exp(-mx) if sink else 0.0) + e.sum())
             out[i, hh] = pr @ v[lo:i + 1, g]
     return out.reshape(T, H * dv) @ W[p + "o"].T
 
