@@ -181,7 +181,7 @@ def test_chunked_sink_attention_alone(case, f32):
                     other = ro.chunk_sink_attention(h.to(F64), W64, "", dict(m, mask={"size": size}), eps)
                     assert float(row_errors(other, want).max()) > 30 * TOL[True]
         nosink = ro.chunk_sink_attention(h.to(F64), W64, "", m, eps, sink=False)
-        assert float(row_errors(nosink, want).median()) > 10 * TOL[True]
+        assert float(row_errors(nosink, want).max()) > 0.1        # the first positions of a chunk see few keys: there the sink weighs most
 
 
 LATENT_CASES = {
@@ -221,9 +221,12 @@ def test_windowed_rotary_latent_attention_alone(case, f32):
                 if size != window:
                     other = ro.windowed_latent_attention(h.to(F64), W64, "", dict(m, mask={"size": size}), eps)
                     assert float(row_errors(other, want).max()) > 30 * TOL[True]
-        if window > 1:      # the rotary part matters: the same rows two positions later answer differently
-            shifted = ro.windowed_latent_attention(torch.cat([h[:2], h]).to(F64), W64, "", m, eps)[2:]
-            assert float(row_errors(shifted[window:], want[window:]).median()) > 10 * TOL[True]
+        if window > 1 and E > 2:      # positions enter the scores: another rotary base, or the table without its scaling, is another
+            # function (a single pair turns at frequency 1 whatever the base)
+            for rot in (dict(m["rot"], base=3.0 * m["rot"]["base"]), {k: v for k, v in m["rot"].items() if k != "scaling"}):
+                if rot != m["rot"]:
+                    other = ro.windowed_latent_attention(h.to(F64), W64, "", dict(m, rot=rot), eps)
+                    assert float(row_errors(other, want).median()) > 10 * TOL[True]
         nogate = dict(W64)
         nogate["g"] = torch.zeros_like(W64["g"])
         assert float(row_errors(ro.windowed_latent_attention(h.to(F64), nogate, "", m, eps), want).median()) > 10 * TOL[True]
@@ -413,7 +416,8 @@ def test_streams_of_one_with_weights_and_no_layers():
     bare = cases.config(23, 12, [], streams=2, embed_scale=0.5, logit_scale=3.0)
     Wb = cases.weights(bare, seed=15)
     eng = make_engine(bare, Wb, True)
-    assert float(row_errors(run_schedule(eng, toks[:9], [4]), ro.forward(bare, Wb, toks[:9])).max()) < TOL[True]
+    few = cases.tokens(bare, 9)
+    assert float(row_errors(run_schedule(eng, few, [4]), ro.forward(bare, Wb, few)).max()) < TOL[True]
     eng.close_all()
 
 
