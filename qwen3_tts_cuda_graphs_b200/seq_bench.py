@@ -1,7 +1,8 @@
 """Throughput of a sequence model at layer sizes that resemble a real model's, beside the closest model of the framework.
 
 `bench.py --seq-model` (the default workload of bench.py is untouched).  Random weights, synthetic tokens.  Sizes w* are Sidalorn
-models, r* Redodra models (`--seq-sizes r1024,w1024` puts the two designs side by side at equal width).  For each size:
+models, r* Redodra models, z* Ratizen models (`--seq-sizes z1024,r1024,w1024` puts the designs side by side at equal width).  For
+each size:
   * prefill: one step of T prompt tokens through `SequenceEngine.step` (tokens / s), and the same in portions;
   * decode: single-token steps at context T (tokens / s), replayed as CUDA graphs as the generation path does;
   * per op kind: device time of every op of the step's list launched alone (CUDA events, L2 flushed before each timed
@@ -21,15 +22,16 @@ from collections import defaultdict
 import torch
 
 from . import codec as K
-from .config import (DeltaRuleConfig, DenseFFConfig, LatentAttentionConfig, MoEFFConfig, ParallelMixerConfig, RedodraConfig, RglruConfig,
-                     SeqLayerConfig, SidalornConfig, SoftmaxAttentionConfig, StateSpaceConfig)
+from .config import (DeltaRuleConfig, DenseFFConfig, LatentAttentionConfig, MoEFFConfig, ParallelMixerConfig, RatizenConfig, RedodraConfig,
+                     RglruConfig, SeqLayerConfig, SidalornConfig, SoftmaxAttentionConfig, StateSpaceConfig)
 
 KIND_NAMES = {K.K_GEMM: "gemm (tcgen05 / gemv)", K.K_RMSNORM: "rmsnorm", K.K_ATTN: "attention (prefill, CUDA cores)", 8: "qk-norm + rope + kv",
               K.K_EMBED: "embed / gather", K.K_TCONV: "time conv", K.K_GNORM: "group norm", K.K_BDGEMM: "block-diagonal product",
               K.K_LATENT_ATTN: "latent attention", K.K_LRU_SCAN: "lru scan", K.K_POLYNORM: "polynorm", K.K_ROUTER: "router",
               K.K_MOE_SORT: "moe sort", K.K_GGEMM: "grouped expert product", K.K_MOE_COMBINE: "moe combine", K.K_COMMIT: "state commit",
               K.K_DYT: "dynamic-tanh norm", K.K_DEPTH_MIX: "depth mix", K.K_XIELU: "xielu", K.K_ROT_APPEND: "rotary + cache append",
-              K.K_CACHE_ATTN: "cached softmax attention", K.K_MSTATE_SCAN: "matrix-state scan"}
+              K.K_CACHE_ATTN: "cached softmax attention", K.K_MSTATE_SCAN: "matrix-state scan", K.K_HYPER: "residual streams (+ norm)",
+              K.K_GLU: "gated unit"}
 
 
 def peaks():
@@ -68,7 +70,17 @@ def sizes():
             layers.append(SeqLayerConfig(t, mix[t], DenseFFConfig(ff)))
         return RedodraConfig(vocab, width, 1e-5, tuple(layers))
 
-    return {"w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1),
+    def ratizen(width, heads, kv, rank, q_rank, experts, top, expert_ff, shared_ff, order, span=1024, streams=4, vocab=3072):
+        att = SoftmaxAttentionConfig(heads, kv, 128, 128, 128 ** -0.5, chunk=span, qk_norm=True, zero_sink=True)
+        lat = LatentAttentionConfig(16, 128, 128, rank, 192 ** -0.5, q_rank=q_rank, rot_dim=64, rot_base=5e5, rot_scaling=(4.0, 4096.0, 16.0, 2.0),
+                                    window=span, gate=True, sink=False)
+        moe = MoEFFConfig(experts, 0, top, 1, 1, 1.0, expert_ff, shared_ff, score="sigmoid", renorm=False, weight_input=True, gated=True)
+        layers = tuple(SeqLayerConfig(t, att if t == "attention" else lat, moe) for t in order)
+        return RatizenConfig(vocab, width, 1e-5, 2.0, 0.7, streams, True, 0.3, layers)
+
+    return {"z1024": ratizen(1024, 16, 4, 256, 384, 16, 2, 768, 1536, ("attention", "latent_attention", "latent_attention") * 2),
+            "z2048": ratizen(2048, 32, 8, 512, 768, 32, 4, 1024, 2048, ("attention", "latent_attention", "latent_attention")),
+            "w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1),
             "r1024": redodra(1024, 16, 4, 512, 16, 64, 3072, ("delta", "attention", "parallel", "shared", "delta", "parallel")),
             "r2048": redodra(2048, 32, 8, 1024, 32, 64, 6144, ("delta", "attention", "parallel"))}
 
@@ -78,6 +90,10 @@ def random_model(cfg, device, seed=0):
         from .redodra import RedodraModel, init_synthetic
 
         return RedodraModel(cfg, init_synthetic(cfg, seed).get, device, f32=False)
+    if isinstance(cfg, RatizenConfig):
+        from .ratizen import RatizenModel, init_synthetic
+
+        return RatizenModel(cfg, init_synthetic(cfg, seed).get, device, f32=False)
     from .sidalorn import SidalornModel, tensor_specs
 
     g = torch.Generator(device=device).manual_seed(seed)
@@ -110,19 +126,26 @@ def op_cost(o, ctx_keys: float):
     if k == K.K_GGEMM:
         return 2.0 * M * N * o.K, o.i0 * N * o.K * ws + M * o.K * ws + M * N * outs
     if k == K.K_LATENT_ATTN:
-        return 4.0 * M * o.i0 * o.i1 * ctx_keys, ctx_keys * o.i1 * ws + 2 * M * N * 4
+        keys = min(ctx_keys, o.a_rows) if o.a_rows > 0 else ctx_keys        # a sliding window bounds the keys of a query
+        return 2.0 * M * o.i0 * (2 * o.i1 + o.cin) * keys, min(ctx_keys + M / 2, keys + M) * (o.i1 + o.cin) * ws + 2 * M * N * 4
     if k == K.K_ATTN:
         return 4.0 * M * o.i0 * o.i2 * ctx_keys, M * (o.i0 + 2 * o.i1) * o.i2 * 2 + M * o.i0 * o.i2 * 2
     if k == K.K_LRU_SCAN:
         return 0.0, M * N * (4 * 4 + outs)
     if k == K.K_CACHE_ATTN:
         keys = min(ctx_keys, o.K + o.a_rows) if o.K > 0 else ctx_keys
+        if o.tap_off[0] > 0:
+            keys = min(keys, (o.tap_off[0] + 1) / 2.0)                      # chunked mask: half a chunk on average
         return 2.0 * M * o.i0 * (o.i2 + o.cin) * keys, min(ctx_keys + M / 2, keys + M) * o.i1 * (o.i2 + o.cin) * ws + M * o.i0 * (o.i2 * 4 + o.cin * outs)
     if k == K.K_MSTATE_SCAN:
         per = 7.0 if o.taps == 0 else 5.0
         return per * M * o.i0 * o.i2 * o.cin, M * (2 * o.i1 * o.i2 + 2 * o.i0 * o.cin) * 4 + 2 * o.i0 * o.i2 * o.cin * 4
     if k == K.K_ROT_APPEND:
         return 0.0, M * (o.i0 * o.i2 * 8 + o.i1 * (o.i2 + o.cin) * (4 + ws))
+    if k == K.K_HYPER:
+        return 0.0, M * N * (4 * o.i0 * (2 if o.res else 1) + (4 if o.res else 0) + (outs if o.C else 0))
+    if k == K.K_GLU:
+        return 0.0, M * N * (8 + outs)
     if k == K.K_DEPTH_MIX:
         return 0.0, M * N * 4 * (o.i0 + 1)
     if k == K.K_COMMIT:
@@ -230,6 +253,13 @@ def bench_sequence_model(name, cfg, T, device):
     for i, (L, w) in enumerate(zip(cfg.layers, model.layers)):
         if isinstance(cfg, RedodraConfig):
             wb += operand_bytes(w)
+            continue
+        if isinstance(cfg, RatizenConfig):
+            wb += operand_bytes(w["mix"])
+            f = w.get("ff")
+            if f:
+                wb += (f["up"][0].numel() + f["down"][0].numel()) * 2 * min(L.mlp.top, L.mlp.experts) + operand_bytes(f["router"])
+                wb += sum(operand_bytes(f[k]) for k in ("shared_up", "shared_down"))
             continue
         for k, t in w["mix"].items():
             wb += t.numel() * t.element_size() if t is not None else 0
