@@ -89,7 +89,11 @@ enum fq3c_kind {
                          positions of one expert are in token order                                                            */
   FQ3C_GGEMM = 21,    /* grouped product over sorted rows: for expert e and positions p in [seg[e], seg[e + 1]):
                          C[p, :N] = epi(sum_k A[rows ? rows[p] : p, k] * B[e][n][k]); seg = p0 (int32 [i0 + 1]), rows = p1 (int32) or
-                         NULL, i0 experts, M = upper bound of positions.  A bf16, or f32 with FQ3C_A_F32; B bf16, F32: both f32     */
+                         NULL, i0 experts, M = upper bound of positions.  A bf16, or f32 with FQ3C_A_F32; B bf16, F32: both f32.
+                         ABI 8: FQ3C_SWIGLU: B's rows alternate (gate_n, up_n) and C[p, n] = silu(w gate) * (w up) is N / 2 columns
+                         wide; w = 1, or scale[p] (f32), or, with ws (int32 [tokens, i1] sorted position of every choice) and
+                         scale = f32 [tokens, i1], the weight of the choice that sits at p (it multiplies the expert's input).
+                         FQ3C_GEMM takes FQ3C_SWIGLU the same way (w = 1)                                                         */
   FQ3C_MOE_COMBINE = 22, /* C f32 [M, N] = sum_j w[m, j] * (ids[m, j] >= i1 ? x[m, :] : Y[pos[m, j], :]) (+ res[m, :]);
                          A = Y f32, B = x f32 [M, ldr] (identity experts), p0 = ids int32 [M, i0], p1 = w f32 [M, i0],
                          ws = pos int32 [M, i0], res = f32 [M, ldr] or NULL (shared expert).  ABI 8: p1 may be NULL (every w = 1:

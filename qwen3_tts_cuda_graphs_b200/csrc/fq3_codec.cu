@@ -987,13 +987,15 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, u
 }
 
 // ---- sequence-model ops: launch logic ---------------------------------------------------------------------------------------
-constexpr int SEQ_GEMM_FLAGS = FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID | FQ3C_OUT_F32 | FQ3C_F32 | FQ3C_NOROUND | FQ3C_A_F32;
+constexpr int SEQ_GEMM_FLAGS = FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID | FQ3C_OUT_F32 | FQ3C_F32 | FQ3C_NOROUND | FQ3C_A_F32 | FQ3C_SWIGLU;
 
 // a_f32 / b_f32: operand types.  exact: keep f32 A values as they are (CUDA cores) instead of rounding them onto the tensor cores.
 int launch_seq_gemm(const SeqGemm& g, bool a_f32, bool b_f32, bool exact, int zcount, int row_tiles, cudaStream_t s) {
   if (g.flags & ~SEQ_GEMM_FLAGS) return fail("sequence product: unsupported epilogue flag");
   if (b_f32 && !a_f32) return fail("sequence product: f32 weights need f32 rows");
   if (g.M <= 0 || g.N <= 0 || g.K <= 0 || zcount <= 0) return 0;
+  if ((g.flags & FQ3C_SWIGLU) && ((g.N & 1) || (g.flags & (FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID)) || zcount != 1))
+    return fail("sequence product: a gated-unit epilogue takes an even number of alternating gate / up columns and no other epilogue");
   const size_t gemv_smem = (size_t)g.M * g.K * sizeof(float);
   if (!g.seg && g.M <= 8 && gemv_smem <= 96 * 1024) {
     static bool attr[64] = {};
@@ -1080,6 +1082,8 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       g.M = o.M; g.N = o.N; g.K = o.K; g.lda = o.lda; g.ldb = o.K; g.ldc = o.ldc; g.flags = o.flags & ~FQ3C_BIAS;
       g.a_mod = 1; g.seg = reinterpret_cast<const int*>(o.p0); g.rows = reinterpret_cast<const int*>(o.p1); g.E = o.i0;
       g.b_estride = (long long)o.N * o.K;
+      if (o.flags & FQ3C_SWIGLU) { g.rs_w = reinterpret_cast<const float*>(o.scale); g.rs_pos = reinterpret_cast<const int*>(o.ws); g.rs_top = o.i1; }
+      if (g.rs_pos && (!g.rs_w || !g.rows || g.rs_top < 1)) return fail("ggemm: a router's weights need the choices' places, the row list and the choice count");
       const bool f32 = (o.flags & FQ3C_F32) != 0;
       return launch_seq_gemm(g, f32 || (o.flags & FQ3C_A_F32), f32, false, 1, (o.M + 63) / 64 + o.i0, s);
     }

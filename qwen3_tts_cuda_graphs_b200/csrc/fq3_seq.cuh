@@ -47,7 +47,27 @@ struct SeqGemm {
   int M, N, K, lda, ldb, ldc, flags;
   int a_mod, a_zstride, c_zstride; long long b_zstride;   // grid.z: A columns (z % a_mod) * a_zstride, B + z * b_zstride, C columns z * c_zstride
   const int* seg; const int* rows; int E; long long b_estride;
+  // FQ3C_SWIGLU: the weight rows alternate (gate_n, up_n), so columns (2n, 2n + 1) of the product are one gated unit and the output
+  // is C[r, n] = silu(w gate) * (w up), N / 2 columns wide.  w = 1, or rs_w[r], or (rs_pos given: a router's choices) the weight
+  // rs_w[m, j] of the choice j of token m = rows[r] whose sorted position rs_pos[m, j] is r.
+  const float* rs_w; const int* rs_pos; int rs_top;
 };
+__device__ __forceinline__ float sg_row_scale(const SeqGemm& g, const int r) {
+  if (!g.rs_w) return 1.f;
+  if (!g.rs_pos) return g.rs_w[r];
+  const int m = g.rows ? g.rows[r] : r;
+  for (int j = 0; j < g.rs_top; ++j)
+    if (g.rs_pos[(size_t)m * g.rs_top + j] == r) return g.rs_w[(size_t)m * g.rs_top + j];
+  return 1.f;
+}
+__device__ __forceinline__ void sg_store_glu(const SeqGemm& g, const int r, const int ccol, const int n_even, const float gate, const float up,
+                                             const float w) {
+  const float a = w * gate, b = w * up;
+  const float v = a / (1.f + expf(-a)) * b;
+  const size_t ci = (size_t)r * g.ldc + ccol + (n_even >> 1);
+  if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
+  else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
+}
 constexpr int SG_BM = 64, SG_BN = 64, SG_BK = 16;
 
 template <typename TA, typename TB>
@@ -110,6 +130,15 @@ __global__ void __launch_bounds__(256) fq3s_gemm_kernel(const SeqGemm g) {
   for (int i = 0; i < 4; ++i) {
     const int r = row0 + ty * 4 + i;
     if (r >= row_end) continue;
+    if (g.flags & FQ3C_SWIGLU) {
+      const float w = sg_row_scale(g, r);
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int n = col0 + tx * 4 + j;
+        if (n + 1 < g.N) sg_store_glu(g, r, ccol, n, acc[i][j], acc[i][j + 1], w);
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = col0 + tx * 4 + j;
@@ -243,6 +272,22 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
     __syncthreads();
   }
   const int ccol = z * g.c_zstride;
+  if (g.flags & FQ3C_SWIGLU) {      // an accumulator pair (q, q + 1) is one gated unit
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int q = 0; q < 4; q += 2) {
+        const int r = row0 + wm + i * 16 + (lane >> 2) + (q >> 1) * 8;
+        if (r >= row_end) continue;
+        const float w = sg_row_scale(g, r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = col0 + wn + j * 8 + (lane & 3) * 2;
+          if (n + 1 < g.N) sg_store_glu(g, r, ccol, n, acc[i][j][q], acc[i][j][q + 1], w);
+        }
+      }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -337,6 +382,22 @@ __global__ void __launch_bounds__(256) fq3s_gemm_mma128_kernel(const SeqGemm g) 
     __syncthreads();
   }
   const int ccol = z * g.c_zstride;
+  if (g.flags & FQ3C_SWIGLU) {      // an accumulator pair (q, q + 1) is one gated unit
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int q = 0; q < 4; q += 2) {
+        const int r = row0 + wm + i * 16 + (lane >> 2) + (q >> 1) * 8;
+        if (r >= row_end) continue;
+        const float w = sg_row_scale(g, r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = col0 + wn + j * 8 + (lane & 3) * 2;
+          if (n + 1 < g.N) sg_store_glu(g, r, ccol, n, acc[i][j][q], acc[i][j][q + 1], w);
+        }
+      }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -448,6 +509,19 @@ __global__ void __launch_bounds__(256) fq3s_gemv_kernel(const SeqGemm g) {
     }
   }
   const int ccol = z * g.c_zstride;
+  if (g.flags & FQ3C_SWIGLU) {      // warps (2k, 2k + 1) hold a unit's gate and up columns: the odd one hands its sums over
+    __shared__ float ex[8][8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      if (m >= g.M) break;
+      acc[m] = warp_sum(acc[m]);
+      if ((warp & 1) && lane == 0) ex[warp][m] = acc[m];
+    }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp >> 1)) : "memory");
+    if (!(warp & 1) && lane == 0 && n + 1 < g.N)
+      for (int m = 0; m < g.M; ++m) sg_store_glu(g, m, ccol, n, acc[m], ex[warp + 1][m], sg_row_scale(g, m));
+    return;
+  }
 #pragma unroll
   for (int m = 0; m < 8; ++m) {
     if (m >= g.M) break;
@@ -513,6 +587,13 @@ __global__ void __launch_bounds__(256) fq3s_ggemv_kernel(const SeqGemm g) {
     for (int k = lane; k < g.K; k += 32) acc = fmaf(ldf<TB>(w + k), xs[k], acc);
   }
   float v = warp_sum(acc);
+  if (g.flags & FQ3C_SWIGLU) {
+    __shared__ float ex[8];
+    if ((warp & 1) && lane == 0) ex[warp] = v;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp >> 1)) : "memory");
+    if (!(warp & 1) && lane == 0 && n + 1 < g.N) sg_store_glu(g, p, 0, n, v, ex[warp + 1], sg_row_scale(g, p));
+    return;
+  }
   if (lane == 0) {
     if (g.flags & FQ3C_GELU) v = gelu_f(v);
     if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);

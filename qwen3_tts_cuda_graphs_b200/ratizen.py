@@ -26,9 +26,6 @@ from .config import LatentAttentionConfig, MoEFFConfig, RatizenConfig, SoftmaxAt
 from .seq_ops import StepBuilder
 from .seq_state import StateSpec
 
-EXPERT_PARTS = ("gate", "up", "down")
-
-
 def _expert_specs(p: str, ff: int, W: int) -> Dict[str, tuple]:
     return {p + "gate": (ff, W), p + "up": (ff, W), p + "down": (W, ff)}
 
@@ -140,11 +137,16 @@ class Packer:
 
     def moe(self, p: str, f: MoEFFConfig) -> dict:
         raw = self.raw
+
+        def pair(q):      # rows (gate_0, up_0, gate_1, up_1, ...): a product's neighbouring columns are one gated unit
+            g, u = raw(q + "gate"), raw(q + "up")
+            return torch.stack([g, u], 1).reshape(2 * g.shape[0], g.shape[1])
+
         d = {"router": self.W(raw(p + "router")), "correction": None,
-             "up": self.W(torch.stack([torch.cat([raw(f"{p}e{e}.gate"), raw(f"{p}e{e}.up")], 0) for e in range(f.experts)])),
+             "up": self.W(torch.stack([pair(f"{p}e{e}.") for e in range(f.experts)])),
              "down": self.W(torch.stack([raw(f"{p}e{e}.down") for e in range(f.experts)])), "shared_up": None, "shared_down": None}
         if f.shared_ff:
-            d["shared_up"] = self.W(torch.cat([raw(p + "shared.gate"), raw(p + "shared.up")], 0))
+            d["shared_up"] = self.W(pair(p + "shared."))
             d["shared_down"] = self.W(raw(p + "shared.down"))
         return d
 

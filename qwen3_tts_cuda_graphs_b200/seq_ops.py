@@ -24,7 +24,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .codec import (F_A_F32, F_BIAS, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RAW_WEIGHTS, F_RESID, F_SIGMOID, F_SILU,
+from .codec import (F_A_F32, F_BIAS, F_SWIGLU, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RAW_WEIGHTS, F_RESID, F_SIGMOID, F_SILU,
                     K_BDGEMM, K_CACHE_ATTN, K_COMMIT, K_DEPTH_MIX, K_DYT, K_EMBED, K_GEMM, K_GGEMM, K_GLU, K_GNORM, K_HYPER, K_LATENT_ATTN,
                     K_LRU_SCAN, K_MOE_COMBINE, K_MOE_SORT, K_MSTATE_SCAN, K_POLYNORM, K_ROT_APPEND, K_ROUTER, K_TCONV, K_XIELU, Op, _Plan)
 from .config import DeltaRuleConfig, LatentAttentionConfig, MoEFFConfig, RglruConfig, SoftmaxAttentionConfig, StateSpaceConfig
@@ -138,15 +138,18 @@ class StepBuilder:
         return out
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
-               rows: Optional[int] = None, force_f32: bool = False):
-        """out = act(x W^T + bias).  x and W share a type (bf16, or f32 for true 32-bit: `force_f32` for a router)."""
+               rows: Optional[int] = None, force_f32: bool = False, glu: bool = False):
+        """out = act(x W^T + bias).  x and W share a type (bf16, or f32 for true 32-bit: `force_f32` for a router).  glu: W's rows
+        alternate (gate_n, up_n) and out [M, N / 2] = silu(gate) * up, formed in the product's epilogue."""
         M = rows or self.M
         N, K = w.shape
         f32 = w.dtype == torch.float32
         assert x.dtype == w.dtype, (x.dtype, w.dtype)
         flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_GELU if gelu else 0) | (F_F32 if f32 else 0)
-        if out.dtype == torch.float32 or M <= 4:
+        if out.dtype == torch.float32 or M <= 4 or glu:
             flags |= F_NOROUND      # f32 results stay unrounded; with a few rows the flag also picks the weight-streaming product
+        if glu:
+            flags |= F_SWIGLU
         kw = dict(M=M, N=N, K=K, taps=1, cin=K, a_rows=x.shape[0], lda=x.shape[1], ldc=out.shape[1], col_mod=N, A=x, B=w, C=out, flags=flags)
         if bias is not None:
             kw["bias"] = bias
@@ -372,8 +375,9 @@ class StepBuilder:
     def moe_ff(self, x32: torch.Tensor, xop: torch.Tensor, c: MoEFFConfig, w: dict, out: torch.Tensor):
         """x32: the f32 rows (identity experts); xop: the same rows as product operands.  w: router [n, width], correction f32 [n]
         or None, up [E, ff, width], down [E, width, ff], shared_up / shared_down or None.  Gated experts (c.gated): up is
-        [E, 2 ff, width] and shared_up [2 shared_ff, width], gate rows first, then up rows; the unit is silu(gate) * up, and with
-        c.weight_input the choice's weight multiplies both (the expert's input) instead of the expert's output.  The router's logits are f32 either way:
+        [E, 2 ff, width] and shared_up [2 shared_ff, width] with alternating rows (gate_0, up_0, gate_1, ...); the unit
+        silu(gate) * up is formed in the products' epilogues, and with c.weight_input the choice's weight multiplies both (the
+        expert's input) instead of the expert's output.  The router's logits are f32 either way:
         f32 router weights take the f32 rows (true 32-bit product); bf16 ones take the bf16 rows, whose products with the weights
         are exact in f32 and are summed in f32."""
         M, n, top, E = self.M, c.routed, c.top, c.experts
@@ -397,10 +401,9 @@ class StepBuilder:
         f32 = xop.dtype == torch.float32
         act = self.buf("moe.act", M * top, ff, self.adt)
         if c.gated:
-            gu = self.buf("moe.gu", M * top, 2 * ff)
-            self._op(K_GGEMM, M=M * top, N=2 * ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=gu, ldc=2 * ff,
-                     flags=F_OUT_F32 | (F_F32 if f32 else 0))
-            self.glu(gu, act, pairs=M * top, place=pos, weight=wt if c.weight_input else None)
+            kw = dict(scale=wt, ws=pos, i1=top) if c.weight_input else {}
+            self._op(K_GGEMM, M=M * top, N=2 * ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=act, ldc=ff,
+                     flags=F_SWIGLU | self._oflag(act) | (F_F32 if f32 else 0), **kw)
         else:
             assert not c.weight_input
             self._op(K_GGEMM, M=M * top, N=ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=act, ldc=ff,
@@ -410,8 +413,7 @@ class StepBuilder:
                  flags=F_OUT_F32 | (F_F32 if f32 else 0))
         sh = None
         if w.get("shared_up") is not None and c.gated:
-            sg = self.linear(xop, w["shared_up"], self.buf("moe.sg", M, w["shared_up"].shape[0]))
-            sa = self.glu(sg, self.buf("moe.sa", M, w["shared_up"].shape[0] // 2, self.adt))
+            sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0] // 2, self.adt), glu=True)
             sh = self.linear(sa, w["shared_down"], self.buf("moe.sh", M, width))
         elif w.get("shared_up") is not None:
             sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0], self.adt), gelu=True)

@@ -73,7 +73,9 @@ def test_packing_and_state_declaration_follow_the_layers():
     # first projection: query latent, key / value latent with the rotary key part, gate rows
     assert torch.equal(m.layers[0]["mix"]["wqd"], torch.cat([W["l0.mix.dq"], W["l0.mix.dkv"], W["l0.mix.g"]]))
     ff = m.layers[0]["ff"]
-    assert ff["up"].shape == (5, 24, 40) and torch.equal(ff["up"][2, :12], W["l0.mlp.e2.gate"]) and torch.equal(ff["up"][2, 12:], W["l0.mlp.e2.up"])
+    # an expert's gate and up rows alternate: a product's neighbouring columns form one gated unit
+    assert ff["up"].shape == (5, 24, 40) and torch.equal(ff["up"][2, 0::2], W["l0.mlp.e2.gate"]) and torch.equal(ff["up"][2, 1::2], W["l0.mlp.e2.up"])
+    assert torch.equal(ff["shared_up"][0::2], W["l0.mlp.shared.gate"]) and torch.equal(ff["shared_up"][1::2], W["l0.mlp.shared.up"])
     assert m.layers[1]["ff"]["shared_up"] is None and "ff" not in m.layers[2]
     with pytest.raises(ValueError):
         RatizenModel(sequence_config_from_dict(cfg), {**W, "l1.mix.q": W["l1.mix.q"][:-1]}.get, "cpu")

@@ -140,6 +140,23 @@ def test_embedding_is_scaled_and_copied_into_every_stream():
             assert torch.allclose(X[s].cpu(), table[ids.long()] * 1.7, rtol=1e-6)
 
 
+def test_gated_unit_alone_with_row_weights_and_places():
+    torch.manual_seed(1)
+    gu = torch.randn(6, 2 * 13) * 2
+    out = torch.zeros(6, 13, device=DEV)
+    Bench([]).run(6, lambda b: b.glu(cuda(gu), out))
+    want = ro.silu(gu[:, :13].to(F64)) * gu[:, 13:].to(F64)
+    assert torch.allclose(out.cpu().to(F64), want, atol=1e-5)
+    place, w = torch.tensor([4, -1, 0, 2], dtype=torch.int32), torch.tensor([0.3, 9.0, 1.5, 0.7])
+    out2 = torch.full((6, 13), 7.0, device=DEV)
+    Bench([]).run(6, lambda b: b.glu(cuda(gu), out2, pairs=4, place=cuda(place, torch.int32), weight=cuda(w)))
+    for q, r in enumerate(place.tolist()):
+        if r >= 0:
+            wq = float(w[q])
+            assert torch.allclose(out2[r].cpu().to(F64), ro.silu(wq * gu[r, :13].to(F64)) * (wq * gu[r, 13:].to(F64)), atol=1e-5)
+    assert bool((out2[[1, 3, 5]] == 7.0).all())       # rows nobody names stay as they were
+
+
 CHUNK_CASES = {
     # name: (H, G, d, dv, chunk, width, T, portions, peaky)
     "grouped_heads_small_chunk": (6, 2, 10, 7, 9, 24, 70, [1, 2, 40, 17], 4.0),
