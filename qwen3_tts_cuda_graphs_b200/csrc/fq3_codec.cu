@@ -1033,14 +1033,19 @@ int launch_seq_gemm(const SeqGemm& g, bool a_f32, bool b_f32, bool exact, int zc
   // tall bf16 products (many rows per block / per expert, wide enough outputs): 128 x 128 tiles
   if (!b_f32 && !(a_f32 && exact) && g.N >= 128 && (g.seg ? g.M >= 96 * g.E : g.M >= 256)) {
     dim3 grid128((g.N + 127) / 128, (g.M + 127) / 128 + (g.seg ? g.E : 0), zcount);
-    if (a_f32) fq3s_gemm_mma128_kernel<float><<<grid128, 256, 0, s>>>(g);
+    const bool glu = (g.flags & FQ3C_SWIGLU) != 0;
+    if (a_f32 && glu) fq3s_gemm_mma128_kernel<float, true><<<grid128, 256, 0, s>>>(g);
+    else if (a_f32) fq3s_gemm_mma128_kernel<float><<<grid128, 256, 0, s>>>(g);
+    else if (glu) fq3s_gemm_mma128_kernel<bf16, true><<<grid128, 256, 0, s>>>(g);
     else fq3s_gemm_mma128_kernel<bf16><<<grid128, 256, 0, s>>>(g);
     return 0;
   }
   dim3 grid((g.N + 63) / 64, row_tiles, zcount);
   if (b_f32) fq3s_gemm_kernel<float, float><<<grid, 256, 0, s>>>(g);
   else if (a_f32 && exact) fq3s_gemm_kernel<float, bf16><<<grid, 256, 0, s>>>(g);
+  else if (a_f32 && (g.flags & FQ3C_SWIGLU)) fq3s_gemm_mma_kernel<float, true><<<grid, 128, 0, s>>>(g);
   else if (a_f32) fq3s_gemm_mma_kernel<float><<<grid, 128, 0, s>>>(g);
+  else if (g.flags & FQ3C_SWIGLU) fq3s_gemm_mma_kernel<bf16, true><<<grid, 128, 0, s>>>(g);
   else fq3s_gemm_mma_kernel<bf16><<<grid, 128, 0, s>>>(g);
   return 0;
 }

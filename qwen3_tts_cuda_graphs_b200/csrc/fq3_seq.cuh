@@ -192,7 +192,7 @@ __device__ __forceinline__ void sg_fetch16(const T* p, const bool vec, const int
   r[0] = make_uint4(u[0], u[1], u[2], u[3]);
   r[1] = make_uint4(u[4], u[5], u[6], u[7]);
 }
-template <typename TA>
+template <typename TA, bool GLU = false>      // GLU: the gated-unit epilogue (a variant of its own, so that the plain one compiles as it always did)
 __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
   constexpr int LD = 32 + 8;
   __shared__ __align__(16) bf16 As[64 * LD];
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
     __syncthreads();
   }
   const int ccol = z * g.c_zstride;
-  if (g.flags & FQ3C_SWIGLU) {      // an accumulator pair (q, q + 1) is one gated unit
+  if constexpr (GLU) {      // an accumulator pair (q, q + 1) is one gated unit
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
 
 // The same product for tall operands (hundreds of rows per block / expert): 128 x 128 x 32 tiles, eight warps of 64 x 32 each, fragments
 // by ldmatrix.  Halves the operand traffic per output of the 64 x 64 kernel and runs 16 MMAs per warp between two barriers.
-template <typename TA>
+template <typename TA, bool GLU = false>
 __global__ void __launch_bounds__(256) fq3s_gemm_mma128_kernel(const SeqGemm g) {
   constexpr int LD = 32 + 8, BM = 128, BN = 128;
   __shared__ __align__(16) bf16 As[BM * LD];
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(256) fq3s_gemm_mma128_kernel(const SeqGemm g) 
     __syncthreads();
   }
   const int ccol = z * g.c_zstride;
-  if (g.flags & FQ3C_SWIGLU) {      // an accumulator pair (q, q + 1) is one gated unit
+  if constexpr (GLU) {      // an accumulator pair (q, q + 1) is one gated unit
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
