@@ -1,4 +1,4 @@
-// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-29): the pieces a decoder-only
+// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-31): the pieces a decoder-only
 // language model with a 32-bit residual stream is lowered to.  Included by fq3_codec.cu inside its anonymous namespace.
 //
 // What is 32-bit here whatever the weights' type: norms, softmax scores and weights, router, recurrent state and everything that

@@ -1,4 +1,4 @@
-"""Mechanisms of the sequence models as op-list fragments (include/fq3_codec.h, kinds 12-23).
+"""Mechanisms of the sequence models as op-list fragments (include/fq3_codec.h, kinds 12-31).
 
 A `StepBuilder` lowers ONE step (M new tokens of the request in one slot) to a flat list of `fq3c_op` records over buffers
 it allocates; the list is handed to `fq3c_run` / replayed as a CUDA graph like the codec's plans.  Each mechanism is a method
