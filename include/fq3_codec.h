@@ -142,7 +142,7 @@ enum fq3c_kind {
                          State read from p0 (f32 [i0, i2, cin]), next state written to C2 (FQ3C_COMMIT installs it); C f32 [M, i0 * cin];
                          ws = f32 [M, round_up(2 * i0 + (taps == 0 ? 2 * i1 * i2 + i1 : 0), 4)]: unit vectors, coefficients, q.k       */,
   /* ---- ABI 8 */
-  FQ3C_HYPER = 30,    /* several residual streams (hyper-connections): X_s = A + s * K elements, s < i0 <= 8 (f32 slices [M, lda] of one
+  FQ3C_HYPER = 30,    /* several residual streams (hyper-connections): X_s = A + s * K elements, s < i0 <= 16 (f32 slices [M, lda] of one
                          buffer).  With res (y = f32 [M, ldr], a sublayer's output): every stream at once from the old ones,
                          X_t <- sum_s p0[s * i0 + t] X_s + f1 * p1[t] * y  (p0 = f32 [i0, i0] indexed [from, to], p1 = f32 [i0]).
                          Then, with C: u = sum_s bias[s] X_s (bias = f32 [i0], the next sublayer's read weights) and

@@ -514,8 +514,8 @@ class RatizenConfig:
                 raise ValueError(f"unknown feed-forward kind {f['kind']!r}")
             layers.append(SeqLayerConfig(L["type"], mixer, mlp))
         streams = int(raw.get("streams", 1))
-        if not 1 <= streams <= 8:
-            raise ValueError("streams must lie in 1 .. 8")
+        if not 1 <= streams <= 16:
+            raise ValueError("streams must lie in 1 .. 16")
         return RatizenConfig(int(raw["vocab"]), int(raw["width"]), float((raw.get("norm") or {}).get("eps", 1e-6)),
                              float((raw.get("embedding") or {}).get("scale", 1.0)), float(raw.get("residual_mult", 1.0)), streams,
                              "streams" in raw, float(raw.get("logit_scale", 1.0)), tuple(layers))

@@ -1271,16 +1271,18 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
     }
     case FQ3C_HYPER: {
       if (o.i0 < 1 || o.i0 > HY_MAX || !o.A || (o.i0 > 1 && o.K < o.N) || (o.res && (!o.p0 || !o.p1)) || (o.C && !o.bias) || (!o.C && !o.res))
-        return fail("hyper: 1 to 8 streams; mixing and write weights with a sublayer output; read weights with an output");
+        return fail("hyper: 1 to 16 streams; mixing and write weights with a sublayer output; read weights with an output");
       if ((size_t)o.N * 4 > 200 * 1024) return fail("hyper: row too wide for shared memory");
       static bool hattr[64] = {};
       int dev = 0;
       cudaGetDevice(&dev);
       if (dev >= 0 && dev < 64 && !hattr[dev]) {
-        cudaFuncSetAttribute(fq3s_hyper_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(fq3s_hyper_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(fq3s_hyper_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         hattr[dev] = true;
       }
-      fq3s_hyper_kernel<<<o.M, 256, (size_t)o.N * 4, s>>>(o);
+      if (o.i0 <= 8) fq3s_hyper_kernel<8><<<o.M, 256, (size_t)o.N * 4, s>>>(o);
+      else fq3s_hyper_kernel<16><<<o.M, 256, (size_t)o.N * 4, s>>>(o);
       return 0;
     }
     case FQ3C_GLU:

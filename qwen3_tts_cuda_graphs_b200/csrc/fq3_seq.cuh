@@ -1979,9 +1979,10 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
 // ABI 8 (kinds 30-31): several residual streams with learned read / write / mixing weights, and the gated unit of routed experts
 // whose weight multiplies the expert's input.
 // ===========================================================================================================================
-constexpr int HY_MAX = 8;
+constexpr int HY_MAX = 16;      // streams; the kernel comes in an 8- and a 16-stream variant (register arrays of that size)
 // grid (M), 256 threads, dynamic shared memory N floats (the row's read-out u).  One pass writes the streams back (when a
 // sublayer's output is given) and forms u; a second one norms it.  Everything f32.
+template <int MAXS>
 __global__ void __launch_bounds__(256) fq3s_hyper_kernel(const fq3c_op o) {
   extern __shared__ float hsm[];
   __shared__ float red[32];
@@ -1993,29 +1994,29 @@ __global__ void __launch_bounds__(256) fq3s_hyper_kernel(const fq3c_op o) {
   const float* wi = reinterpret_cast<const float*>(o.bias);
   float ss = 0.f;
   for (int c = threadIdx.x; c < o.N; c += blockDim.x) {
-    float xs[HY_MAX], xn[HY_MAX];
+    float xs[MAXS], xn[MAXS];
 #pragma unroll
-    for (int s = 0; s < HY_MAX; ++s) xs[s] = s < S ? X[(size_t)s * (size_t)o.K + c] : 0.f;
+    for (int s = 0; s < MAXS; ++s) xs[s] = s < S ? X[(size_t)s * (size_t)o.K + c] : 0.f;
     if (y) {
       const float yv = o.f1 * y[c];
 #pragma unroll
-      for (int t = 0; t < HY_MAX; ++t) {
+      for (int t = 0; t < MAXS; ++t) {
         if (t >= S) continue;
         float acc = wo[t] * yv;
 #pragma unroll
-        for (int s = 0; s < HY_MAX; ++s)
+        for (int s = 0; s < MAXS; ++s)
           if (s < S) acc = fmaf(mix[s * S + t], xs[s], acc);
         xn[t] = acc;
         X[(size_t)t * (size_t)o.K + c] = acc;
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < HY_MAX; ++t) xn[t] = xs[t];
+      for (int t = 0; t < MAXS; ++t) xn[t] = xs[t];
     }
     if (o.C) {
       float u = 0.f;
 #pragma unroll
-      for (int t = 0; t < HY_MAX; ++t)
+      for (int t = 0; t < MAXS; ++t)
         if (t < S) u = fmaf(wi[t], xn[t], u);
       hsm[c] = u;
       ss = fmaf(u, u, ss);

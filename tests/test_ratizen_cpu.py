@@ -32,7 +32,7 @@ def test_config_reader_takes_every_size_and_constant_from_the_dictionary():
     assert (plain.streams, plain.hyper, plain.residual_mult, plain.embed_scale, plain.logit_scale) == (1, False, 1.0, 1.0, 1.0)
     assert "Ratizen" in SEQUENCE_ARCHITECTURES
     for breakit in (lambda d: d["layers"][1]["mixer"].update(kv_heads=4), lambda d: d["layers"][0]["mlp"]["router"].update(top=6),
-                    lambda d: d.update(streams=9), lambda d: d["layers"][0].update(type="other"),
+                    lambda d: d.update(streams=17), lambda d: d["layers"][0].update(type="other"),
                     lambda d: d["layers"][0]["mixer"]["rot"].update(dims=2)):
         bad = cases.odd()
         breakit(bad)

@@ -109,7 +109,7 @@ def layer_weights(cfg, i, seed, peaky=0.0):
 # ---------------------------------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ---------------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("S", [1, 2, 3, 8])
+@pytest.mark.parametrize("S", [1, 2, 3, 8, 11, 16])
 def test_residual_streams_write_read_and_norm(S):
     torch.manual_seed(S)
     M, N, eps, mult = 5, 45, 1e-2, 0.6
