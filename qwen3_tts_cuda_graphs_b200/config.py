@@ -252,6 +252,7 @@ class LatentAttentionConfig:
     q_rank: int = 0          # > 0: queries go through a normed latent of this size too
     rot_dim: int = 0         # > 0: every query head has this many more entries that turn with the position, scored against one
                              #      rotated key part per position shared by all heads (cached beside the latent)
+    rot_dims: int = 0        # leading entries of the rotary part that turn (pairs 2i, 2i + 1); 0: all rot_dim of them
     rot_base: float = 10000.0
     rot_scaling: Optional[Tuple[float, float, float, float]] = None   # (factor, original, fast, slow): scaled rotary table
     window: int = 0          # > 0: position i sees j only if 0 <= i - j < window
@@ -491,12 +492,11 @@ class RatizenConfig:
                 rot = m.get("rot") or {}
                 sc = rot.get("scaling")
                 rot_dim = int(m.get("rot_dim", 0))
-                if rot_dim and int(rot.get("dims", rot_dim)) != rot_dim:
-                    raise ValueError(f"layer {i}: the rotary table must cover the whole rotated part")
-                if rot_dim % 2:
-                    raise ValueError(f"layer {i}: rot_dim must be even")
+                dims = int(rot.get("dims", rot_dim))
+                if dims > rot_dim or dims % 2:
+                    raise ValueError(f"layer {i}: rot.dims must be even and at most rot_dim")
                 mixer = LatentAttentionConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"]),
-                                              q_rank=int(m.get("q_rank", 0)), rot_dim=rot_dim, rot_base=float(rot.get("base", 10000.0)),
+                                              q_rank=int(m.get("q_rank", 0)), rot_dim=rot_dim, rot_dims=0 if dims == rot_dim else dims, rot_base=float(rot.get("base", 10000.0)),
                                               rot_scaling=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None,
                                               window=int(mask.get("size", 0)), gate=True, sink=False)
             else:

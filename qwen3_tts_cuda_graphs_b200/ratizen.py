@@ -129,7 +129,7 @@ class Packer:
         # query up-projection rows: the heads' plain parts first, then the heads' rotary parts
         rows = torch.arange(H * (d + E)).reshape(H, d + E)
         order = torch.cat([rows[:, :d].reshape(-1), rows[:, d:].reshape(-1)])
-        freq, amp = scaled_rotary_table(E, m.rot_base, m.rot_scaling) if E > 0 else (torch.zeros(0), 1.0)
+        freq, amp = scaled_rotary_table(m.rot_dims or E, m.rot_base, m.rot_scaling) if E > 0 else (torch.zeros(0), 1.0)
         return {"wqd": self.W(torch.cat([raw(p + "dq"), raw(p + "dkv"), raw(p + "g")], 0)), "dq_norm": self.F(raw(p + "dq.norm")),
                 "uq": self.W(raw(p + "uq")[order]), "dkv_norm": self.F(raw(p + "dkv.norm")),
                 "uk_t": self.W(raw(p + "uk").reshape(H, d, R).transpose(1, 2)), "uv": self.W(raw(p + "uv").reshape(H, m.vdim, R)),

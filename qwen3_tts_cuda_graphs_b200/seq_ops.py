@@ -179,7 +179,7 @@ class StepBuilder:
         With the options of LatentAttentionConfig (E = rot_dim): wqd = [Q | dkv (rank) | rotary key part (E) | gate rows (H)] where
         Q is the query latent's down-projection (q_rank rows; then dq_norm f32 [q_rank] and uq [H*dim + H*E, q_rank]) or the query
         projection itself, in both cases laid out as all heads' plain parts, then all heads' rotary parts; freq f32 [E / 2] and
-        amp (float): the rotary table.  A cache row is [latent (rank) | rotated key part (E)]."""
+        amp (float): the rotary table (over the first c.rot_dims entries of a rotary part, or all of them).  A cache row is [latent (rank) | rotated key part (E)]."""
         M, H, R, E = self.M, c.heads, c.kv_rank, c.rot_dim
         nq = H * (c.dim + E)
         qcols = c.q_rank if c.q_rank > 0 else nq
@@ -194,7 +194,7 @@ class StepBuilder:
             q, qcol = qd, 0
         if E > 0:   # rotary parts: the heads' query parts turn in place, the one key part goes into the cache behind the latent
             self.plan.keep += [q, qd]
-            self._op(K_ROT_APPEND, M=M, i0=H, i1=1, i2=E, taps=E, cin=0, A=_ptr(q, qcol + H * c.dim), lda=q.shape[1], B=w["freq"],
+            self._op(K_ROT_APPEND, M=M, i0=H, i1=1, i2=E, taps=c.rot_dims or E, cin=0, A=_ptr(q, qcol + H * c.dim), lda=q.shape[1], B=w["freq"],
                      f1=float(w.get("amp", 1.0)), res=qd, norm_ld=qd.shape[1], K=qcols + R, C=_ptr(ctab, R), ldc=ctab.shape[1],
                      p0=self.slot.pos, flags=cf32)
         qa = self.block_linear(q, w["uk_t"], self.buf("la.qa", M, H * R), col=qcol)

@@ -8,8 +8,8 @@ def attn(heads, kv_heads, dim, vdim, chunk, scale):
     return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": chunk}}}
 
 
-def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, window, scale, base=10000.0, scaling=None):
-    rot = {"dims": rot_dim, "base": base}
+def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, window, scale, base=10000.0, scaling=None, dims=None):
+    rot = {"dims": dims or rot_dim, "base": base}
     if scaling is not None:
         rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
     return {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,

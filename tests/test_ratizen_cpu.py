@@ -22,6 +22,9 @@ def test_config_reader_takes_every_size_and_constant_from_the_dictionary():
     assert a == LatentAttentionConfig(3, 6, 5, 12, 0.3, q_rank=10, rot_dim=4, rot_base=500.0, rot_scaling=(3.0, 32.0, 4.0, 1.0), window=7,
                                       gate=True, sink=False)
     assert c.layers[3].mixer.rot_scaling is None and c.layers[3].mixer.window == 1
+    part = cases.odd()
+    part["layers"][0]["mixer"]["rot"]["dims"] = 2         # only the first pair of the four rotary entries turns
+    assert sequence_config_from_dict(part).layers[0].mixer.rot_dims == 2
     b = c.layers[1].mixer
     assert b == SoftmaxAttentionConfig(6, 2, 10, 7, 0.35, chunk=9, qk_norm=True, zero_sink=True)
     assert c.layers[2].mlp is None
@@ -33,7 +36,7 @@ def test_config_reader_takes_every_size_and_constant_from_the_dictionary():
     assert "Ratizen" in SEQUENCE_ARCHITECTURES
     for breakit in (lambda d: d["layers"][1]["mixer"].update(kv_heads=4), lambda d: d["layers"][0]["mlp"]["router"].update(top=6),
                     lambda d: d.update(streams=17), lambda d: d["layers"][0].update(type="other"),
-                    lambda d: d["layers"][0]["mixer"]["rot"].update(dims=2)):
+                    lambda d: d["layers"][0]["mixer"]["rot"].update(dims=6), lambda d: d["layers"][0]["mixer"]["rot"].update(dims=3)):
         bad = cases.odd()
         breakit(bad)
         with pytest.raises(ValueError):

@@ -209,6 +209,7 @@ LATENT_CASES = {
     "sixteen_heads_tensor_core_tiles": (16, 32, 16, 32, 64, 96, 70, (4.0, 64, 16.0, 2.0), 64, 330, [300, 2, 17], 3.0),
     "window_edges_inside_tiles_and_portions": (4, 16, 32, 16, 32, 48, 37, (2.0, 128, 8.0, 1.0), 32, 300, [36, 2, 91, 150], 4.0),
     "wide_rank_two_slices": (4, 16, 16, 8, 272, 32, 150, None, 32, 200, [160, 30], 2.0),
+    "rotary_part_turns_only_in_front": (3, 6, 8, 5, 12, 10, 9, (3.0, 32, 4.0, 1.0), 20, 50, [2, 30], 2.0),
 }
 
 
@@ -220,7 +221,9 @@ def test_windowed_rotary_latent_attention_alone(case, f32):
 
     H, d, E, dv, R, Q, window, scaling, width, T, portions, peaky = LATENT_CASES[case]
     eps = 1e-3
-    cfg = cases.config(8, width, [cases.layer(cases.latent(H, d, E, dv, R, Q, window, 0.9 * (d + E) ** -0.5, base=300.0, scaling=scaling), None)], eps=eps)
+    dims = 4 if case == "rotary_part_turns_only_in_front" else None      # four of the eight rotary entries turn, the rest pass
+    cfg = cases.config(8, width, [cases.layer(cases.latent(H, d, E, dv, R, Q, window, 0.9 * (d + E) ** -0.5, base=300.0, scaling=scaling, dims=dims), None)],
+                       eps=eps)
     W = layer_weights(cfg, 0, seed=len(case), peaky=peaky)
     m = cfg["layers"][0]["mixer"]
     c = sequence_config_from_dict(cfg).layers[0].mixer
