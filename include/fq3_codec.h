@@ -150,7 +150,24 @@ enum fq3c_kind {
                          is NULL, C f32 = u itself (the sum of the streams with bias = ones)                                          */
   FQ3C_GLU = 31       /* gated unit over rows that hold [gate | up]: C[r, c] = silu(w A[r, c]) * (w A[r, N + c]), c < N, A f32 [.., lda];
                          row r = ws[q] (int32 [M], a negative entry skips the row) or q itself, w = p1[q] (f32 [M]) or 1: with both,
-                         q runs over the (token, choice) pairs of a router and w is the choice's weight, applied to the expert's input */
+                         q runs over the (token, choice) pairs of a router and w is the choice's weight, applied to the expert's input */,
+  /* ---- ABI 9 */
+  FQ3C_SUM_NORM = 32  /* the residual sum of a layer whose sublayers all read the same normed input, and the norm that reads the
+                         finished stream: C f32 [M, N] = sum_(j < i0) p0[j] * A_j[m, :], A_j = A + j * K elements (f32 slices [M, lda] of
+                         one buffer; C may be slice 0), p0 = f32 [i0] on the device.  With norm_out: norm_out[m, :] (bf16; f32 with
+                         FQ3C_F32; pitch norm_ld) = n(C[m, :]) * norm_w (f32 [N]), n = v / sqrt(mean(v^2) + norm_eps), or, with
+                         FQ3C_CENTER, (v - mean) / sqrt(mean((v - mean)^2) + norm_eps).  One block per row; the statistics are taken
+                         in two passes over the row kept in shared memory                                                          */
+  /* ABI 9 also adds to existing kinds:
+   *   FQ3C_GNORM: FQ3C_CENTER (the statistics are mean and variance: a layer norm without bias); scale may be NULL (no weights).
+   *   FQ3C_ROT_APPEND: FQ3C_ROT_HALF pairs entry i with entry i + taps / 2 instead of 2i with 2i + 1.
+   *   FQ3C_GEMM / FQ3C_GGEMM: FQ3C_RELU2 epilogue max(z, 0)^2.
+   *   FQ3C_MOE_COMBINE: scale (f32, pitch i2 floats per token), when given: res is multiplied by sigmoid(scale[m * i2]).
+   *   FQ3C_MSTATE_SCAN: taps = 2 (linear attention with a decay per key channel and token): queries of head h at column h * i2,
+   *     keys at K + h * i2, values at a_rows + h * cin of the rows A; decay inputs z of head h at column col_mod + h * i2 of the rows
+   *     res; alpha = sigmoid(z)^f1 = exp(-f1 softplus(-z));  S <- diag(alpha) S + k v^T;  o = f0 S^T q;  i1 = i0;
+   *     ws = f32 [M, round_up(i0 * i2, 4)] (the decays).
+   *     taps = 3 (retention: one fixed decay per head): same columns; S <- scale[h] S + (f0 k) v^T;  o = S^T q; no ws, no res.   */
 };
 
 enum fq3c_flags {
@@ -167,7 +184,11 @@ enum fq3c_flags {
   FQ3C_GATE_PRE = 16384 /* GNORM: the row is multiplied by silu(p1[m, c]) (f32, pitch i1) before its statistics are taken */,
   FQ3C_GATE_POST = 32768 /* GNORM: the normed, weighted row is multiplied by silu(p1[m, c]) */,
   /* ABI 8 */
-  FQ3C_RAW_WEIGHTS = 65536 /* ROUTER: the chosen scores are the weights (times f0), not divided by their sum */
+  FQ3C_RAW_WEIGHTS = 65536 /* ROUTER: the chosen scores are the weights (times f0), not divided by their sum */,
+  /* ABI 9 */
+  FQ3C_RELU2 = 131072   /* GEMM / GGEMM on the sequence products: max(z, 0)^2 */,
+  FQ3C_CENTER = 262144  /* GNORM / SUM_NORM: subtract the mean, divide by the root of the variance (layer norm) */,
+  FQ3C_ROT_HALF = 524288 /* ROT_APPEND: the turning pairs are (i, i + taps / 2) */
 };
 
 typedef struct fq3c_op {

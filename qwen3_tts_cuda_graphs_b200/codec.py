@@ -35,10 +35,12 @@ K_COPY, K_ADVANCE, K_ROLL = 9, 10, 11
  K_COMMIT) = range(12, 24)
 K_DYT, K_DEPTH_MIX, K_XIELU, K_ROT_APPEND, K_CACHE_ATTN, K_MSTATE_SCAN = range(24, 30)
 K_HYPER, K_GLU = 30, 31
+K_SUM_NORM = 32
 F_BIAS, F_GELU, F_RESID, F_SCALE, F_SWIGLU, F_CLAMP, F_OUT_F32, F_SNAKE2, F_SILU = 1, 2, 4, 8, 16, 32, 64, 128, 256
 F_F32, F_NOROUND, F_GELU_TANH, F_SIGMOID, F_A_F32 = 512, 1024, 2048, 4096, 8192
 F_GATE_PRE, F_GATE_POST = 16384, 32768
 F_RAW_WEIGHTS = 65536
+F_RELU2, F_CENTER, F_ROT_HALF = 131072, 262144, 524288
 
 
 class Op(C.Structure):
@@ -148,7 +150,7 @@ def load_lib():
     lib.fq3c_graph_launch.argtypes = [C.c_void_p, C.c_void_p]
     lib.fq3c_graph_destroy.restype = C.c_int
     lib.fq3c_graph_destroy.argtypes = [C.c_void_p]
-    if lib.fq3c_abi_version() != 8:
+    if lib.fq3c_abi_version() != 9:
         raise CodecError("libfq3codec.so ABI version mismatch")
     _lib = lib
     return lib

@@ -289,6 +289,9 @@ class MoEFFConfig:
     renorm: bool = True          # weights = chosen scores / their sum (times scale); False: the chosen scores themselves
     weight_input: bool = False   # the weight multiplies the expert's input instead of its output
     gated: bool = False          # expert = W_down (silu(W_gate x) * W_up x) instead of W_down gelu(W_up x); the shared one too
+    act: str = "gelu"            # activation of an ungated expert: "gelu" | "relu2" (max(z, 0)^2)
+    router_bias: bool = False    # the router's logits have a bias (it enters both the choice and the weights)
+    shared_gate: bool = False    # the shared expert's output is multiplied by sigmoid(w_sg . x), one number per token
 
     @property
     def routed(self) -> int:
@@ -521,11 +524,119 @@ class RatizenConfig:
                              "streams" in raw, float(raw.get("logit_scale", 1.0)), tuple(layers))
 
 
+@dataclass(frozen=True)
+class ChannelDecayAttentionConfig:
+    """Linear attention whose [dim, vdim] state per head decays per key channel and token: alpha = sigmoid(z)^(1/tau), z from a
+    low-rank projection of the input; the read-out is RMS-normed per head, gated by silu and projected."""
+
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    decay_rank: int = 0      # inner size of the low-rank decay projection; 0: whatever the checkpoint's tensors have
+
+
+@dataclass(frozen=True)
+class RetentionConfig:
+    """Linear attention with one fixed decay per head, no softmax and no denominator; queries and keys may turn with the
+    position (pairs i, i + rot_dims / 2); the read-out is divided by its root mean square per head, gated by silu and projected."""
+
+    heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]     # one per head
+    rot_dims: int = 0            # leading entries of each head that turn; 0: no rotation
+    rot_base: float = 10000.0
+
+
+@dataclass(frozen=True)
+class ScaledPairMixerConfig:
+    """Two mixers reading the same input; the result is left_scale * left + right_scale * right."""
+
+    left: SoftmaxAttentionConfig
+    right: ChannelDecayAttentionConfig
+    left_scale: float
+    right_scale: float
+
+
+@dataclass(frozen=True)
+class ZudusunConfig:
+    """Zudusun: one layer norm (weight, no bias) per layer whose output both the mixer and the feed-forward read
+    (x += mixer(h) + ff(h)); mixers in a configured order: softmax attention beside channel-decay linear attention, windowed
+    rotary attention with head norms, biases and a zero-score sink, or retention; feed-forwards of softmax-routed relu^2 experts
+    with a biased router plus a sigmoid-gated shared expert; layers may run another layer's tensors on a state of their own;
+    the output head is the embedding table."""
+
+    architecture = "Zudusun"
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: Tuple[SeqLayerConfig, ...]
+    weights_of: Tuple[int, ...]      # per layer: the layer whose tensors it runs (itself when it has its own)
+
+    @staticmethod
+    def from_dict(raw: dict) -> "ZudusunConfig":
+        layers, owner = [], []
+        n = len(raw["layers"])
+        for i, L in enumerate(raw["layers"]):
+            m = L["mixer"]
+            kind = L["type"]
+            if kind == "parallel":
+                a, r = m["left"], m["right"]
+                left = SoftmaxAttentionConfig(int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a["vdim"]), float(a["scale"]))
+                right = ChannelDecayAttentionConfig(int(r["heads"]), int(r["dim"]), int(r["vdim"]), float(r["tau"]), int(r.get("rank", 0)))
+                mixer = ScaledPairMixerConfig(left, right, float(m.get("left_scale", 1.0)), float(m.get("right_scale", 1.0)))
+                att = left
+            elif kind == "attention":
+                rot, mask = m.get("rot") or {}, m.get("mask") or {}
+                mixer = att = SoftmaxAttentionConfig(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"]), float(m["scale"]),
+                                                     rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)),
+                                                     window=int(mask.get("size", 0)), bias=True, qk_norm=True, zero_sink=True)
+            elif kind == "retention":
+                rot = m.get("rot") or {}
+                mixer = RetentionConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]), tuple(float(d) for d in m["decay"]),
+                                        rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)))
+                att = None
+                if len(mixer.decay) != mixer.heads:
+                    raise ValueError(f"layer {i}: one decay per head")
+                if mixer.rot_dims % 2 or mixer.rot_dims > mixer.dim:
+                    raise ValueError(f"layer {i}: rot.dims must be even and at most dim")
+            else:
+                raise ValueError(f"unknown mixer type {kind!r}")
+            if att is not None:
+                if att.heads % att.kv_heads:
+                    raise ValueError(f"layer {i}: kv_heads must divide heads")
+                if att.rot_dims % 2 or att.rot_dims > att.dim:
+                    raise ValueError(f"layer {i}: rot.dims must be even and at most dim")
+            f = L.get("mlp")
+            if f is None:
+                mlp = None
+            elif f.get("kind", "moe") == "moe":
+                r, sh = f["router"], f.get("shared")
+                mlp = MoEFFConfig(int(r["experts"]), 0, int(r["top"]), 1, 1, 1.0, int(f["expert"]["ff"]), int(sh["ff"]) if sh else 0,
+                                  act="relu2", router_bias=True, shared_gate=bool(sh))
+                if not 1 <= mlp.top <= mlp.experts:
+                    raise ValueError(f"layer {i}: top must lie in 1 .. experts")
+            else:
+                raise ValueError(f"unknown feed-forward kind {f['kind']!r}")
+            j, hops = i, 0
+            while raw["layers"][j].get("weights_of") is not None:      # the layer that holds the tensors
+                j, hops = int(raw["layers"][j]["weights_of"]), hops + 1
+                if not 0 <= j < n or hops > n:
+                    raise ValueError(f"layer {i}: weights_of must lead to a layer that has tensors of its own")
+            if raw["layers"][j]["type"] != kind:
+                raise ValueError(f"layer {i}: weights_of names a layer of another type")
+            owner.append(j)
+            layers.append(SeqLayerConfig(kind, mixer, mlp))
+        return ZudusunConfig(int(raw["vocab"]), int(raw["width"]), float((raw.get("norm") or {}).get("eps", 1e-6)), tuple(layers), tuple(owner))
+
+
 # config.json "architecture" -> (config class, "module:class" of the model that lowers it to op lists)
 SEQUENCE_ARCHITECTURES = {
     "Sidalorn": (SidalornConfig, "sidalorn:SidalornModel"),
     "Redodra": (RedodraConfig, "redodra:RedodraModel"),
     "Ratizen": (RatizenConfig, "ratizen:RatizenModel"),
+    "Zudusun": (ZudusunConfig, "zudusun:ZudusunModel"),
 }
 
 

@@ -59,6 +59,7 @@ __device__ __forceinline__ void epilogue_pair(const fq3c_op& o, int row, int col
     v0 += b[cm0];
     if (has1) v1 += b[cm1];
   }
+  if (o.flags & FQ3C_RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }   // on the f32 sum: one rounding, after the square
   if (!(o.flags & FQ3C_NOROUND)) {
     v0 = bf16r(v0);
     v1 = bf16r(v1);
@@ -130,6 +131,10 @@ __device__ __forceinline__ void epilogue_row8(const fq3c_op& o, int row, int col
     const float* b = reinterpret_cast<const float*>(o.bias);
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] += b[cm[j]];
+  }
+  if (o.flags & FQ3C_RELU2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[j] = fmaxf(v[j], 0.f); v[j] *= v[j]; }
   }
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] = bf16r(v[j]);
@@ -987,14 +992,14 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, u
 }
 
 // ---- sequence-model ops: launch logic ---------------------------------------------------------------------------------------
-constexpr int SEQ_GEMM_FLAGS = FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID | FQ3C_OUT_F32 | FQ3C_F32 | FQ3C_NOROUND | FQ3C_A_F32 | FQ3C_SWIGLU;
+constexpr int SEQ_GEMM_FLAGS = FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID | FQ3C_OUT_F32 | FQ3C_F32 | FQ3C_NOROUND | FQ3C_A_F32 | FQ3C_SWIGLU | FQ3C_RELU2;
 
 // a_f32 / b_f32: operand types.  exact: keep f32 A values as they are (CUDA cores) instead of rounding them onto the tensor cores.
 int launch_seq_gemm(const SeqGemm& g, bool a_f32, bool b_f32, bool exact, int zcount, int row_tiles, cudaStream_t s) {
   if (g.flags & ~SEQ_GEMM_FLAGS) return fail("sequence product: unsupported epilogue flag");
   if (b_f32 && !a_f32) return fail("sequence product: f32 weights need f32 rows");
   if (g.M <= 0 || g.N <= 0 || g.K <= 0 || zcount <= 0) return 0;
-  if ((g.flags & FQ3C_SWIGLU) && ((g.N & 1) || (g.flags & (FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID)) || zcount != 1))
+  if ((g.flags & FQ3C_SWIGLU) && ((g.N & 1) || (g.flags & (FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID | FQ3C_RELU2)) || zcount != 1))
     return fail("sequence product: a gated-unit epilogue takes an even number of alternating gate / up columns and no other epilogue");
   const size_t gemv_smem = (size_t)g.M * g.K * sizeof(float);
   if (!g.seg && g.M <= 8 && gemv_smem <= 96 * 1024) {
@@ -1064,7 +1069,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       fq3s_tconv_kernel<<<dim3((o.N + 255) / 256, o.M + o.taps - 1), 256, 0, s>>>(o);
       return 0;
     case FQ3C_GNORM:
-      if (o.i0 < 1 || o.N % o.i0 || !o.scale || ((o.flags & FQ3C_RESID) && !o.res)) return fail("gnorm: groups must divide N; weights required");
+      if (o.i0 < 1 || o.N % o.i0 || ((o.flags & FQ3C_RESID) && !o.res)) return fail("gnorm: groups must divide N");
       if ((o.flags & (FQ3C_GATE_PRE | FQ3C_GATE_POST)) && !o.p1) return fail("gnorm: gate rows required");
       fq3s_gnorm_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o);
       return 0;
@@ -1290,13 +1295,23 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       fq3s_glu_kernel<<<dim3((o.N + 255) / 256, o.M), 256, 0, s>>>(o);
       return 0;
     case FQ3C_MSTATE_SCAN: {
-      if (o.i0 < 1 || o.i1 < 1 || o.i0 % o.i1 || o.i2 < 1 || o.cin < 1 || !o.A || !o.res || !o.scale || !o.p0 || !o.C || !o.C2 || !o.ws)
-        return fail("mstate_scan: bad configuration");
-      if (o.taps != 0 && o.taps != 1) return fail("mstate_scan: taps selects the delta rule (0) or the state-space scan (1)");
-      if (o.ws_bytes < (int64_t)o.M * mstate_ws_cols(o.i0, o.i1, o.i2, o.taps == 0) * 4) return fail("mstate_scan: workspace too small");
+      if (o.i0 < 1 || o.i1 < 1 || o.i0 % o.i1 || o.i2 < 1 || o.cin < 1 || !o.A || !o.p0 || !o.C || !o.C2) return fail("mstate_scan: bad configuration");
+      if (o.taps < 0 || o.taps > 3)
+        return fail("mstate_scan: taps selects the delta rule (0), the state-space scan (1), a decay per key channel (2) or a fixed decay per head (3)");
       if (o.i2 > 512) return fail("mstate_scan: at most 512 state rows per head");
-      fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
-      count_launches(1);
+      if (o.taps <= 1) {
+        if (!o.res || !o.scale || !o.ws) return fail("mstate_scan: raw projections, A_log and a workspace required");
+        if (o.ws_bytes < (int64_t)o.M * mstate_ws_cols(o.i0, o.i1, o.i2, o.taps == 0) * 4) return fail("mstate_scan: workspace too small");
+      } else if (o.taps == 2) {
+        if (!o.res || !o.ws || o.i1 != o.i0) return fail("mstate_scan: channel decays need their inputs, a workspace and one key head per head");
+        if (o.ws_bytes < (int64_t)o.M * mstate_decay_cols(o.i0, o.i2) * 4) return fail("mstate_scan: workspace too small");
+      } else if (!o.scale || o.i1 != o.i0) {
+        return fail("mstate_scan: fixed decays need one value and one key head per head");
+      }
+      if (o.taps != 3) {
+        fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
+        count_launches(1);
+      }
       dim3 grid((o.cin + MS_COLS - 1) / MS_COLS, o.i0);
       static bool sattr[64] = {};
       int dev = 0;
@@ -1304,13 +1319,37 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       if (dev >= 0 && dev < 64 && !sattr[dev]) {
         cudaFuncSetAttribute(fq3s_mstate_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         cudaFuncSetAttribute(fq3s_mstate_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         sattr[dev] = true;
+      }
+      if (o.taps == 2) {
+        if (o.i2 <= 32) fq3s_mstate_scan_kernel<4, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4, 3), s>>>(o);
+        else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8, 3), s>>>(o);
+        else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16, 3), s>>>(o);
+        else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32, 3), s>>>(o);
+        else fq3s_mstate_scan_kernel<64, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64, 3), s>>>(o);
+        return 0;
       }
       if (o.i2 <= 32) fq3s_mstate_scan_kernel<4><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4), s>>>(o);
       else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8), s>>>(o);
       else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16), s>>>(o);
       else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32), s>>>(o);
       else fq3s_mstate_scan_kernel<64><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64), s>>>(o);
+      return 0;
+    }
+    case FQ3C_SUM_NORM: {
+      if (o.i0 < 1 || !o.A || !o.p0 || !o.C || (o.i0 > 1 && o.K < o.N) || (o.norm_out && !o.norm_w)) return fail("sum_norm: missing operand");
+      if ((size_t)o.N * 4 > 200 * 1024) return fail("sum_norm: row too wide for shared memory");
+      static bool nattr[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !nattr[dev]) {
+        cudaFuncSetAttribute(fq3s_sum_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        nattr[dev] = true;
+      }
+      fq3s_sum_norm_kernel<<<o.M, 256, (size_t)o.N * 4, s>>>(o);
       return 0;
     }
     default: return 1;
@@ -1321,7 +1360,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
 
 extern "C" {
 
-int fq3c_abi_version(void) { return 8; }
+int fq3c_abi_version(void) { return 9; }
 const char* fq3c_last_error(void) { return g_err.c_str(); }
 int64_t fq3c_launch_count(void) { return g_launches.load(); }
 

@@ -1,4 +1,4 @@
-// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-31): the pieces a decoder-only
+// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-32): the pieces a decoder-only
 // language model with a 32-bit residual stream is lowered to.  Included by fq3_codec.cu inside its anonymous namespace.
 //
 // What is 32-bit here whatever the weights' type: norms, softmax scores and weights, router, recurrent state and everything that
@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(256) fq3s_gemm_kernel(const SeqGemm g) {
       if (g.flags & FQ3C_GELU) v = gelu_f(v);
       if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
       if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+      if (g.flags & FQ3C_RELU2) { v = fmaxf(v, 0.f); v *= v; }
       const size_t ci = (size_t)r * g.ldc + ccol + n;
       if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
       else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
@@ -302,6 +303,7 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
         if (g.flags & FQ3C_GELU) v = gelu_f(v);
         if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
         if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+        if (g.flags & FQ3C_RELU2) { v = fmaxf(v, 0.f); v *= v; }
         const size_t ci = (size_t)r * g.ldc + ccol + n;
         if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
         else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
@@ -412,6 +414,7 @@ __global__ void __launch_bounds__(256) fq3s_gemm_mma128_kernel(const SeqGemm g) 
         if (g.flags & FQ3C_GELU) v = gelu_f(v);
         if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
         if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+        if (g.flags & FQ3C_RELU2) { v = fmaxf(v, 0.f); v *= v; }
         const size_t ci = (size_t)r * g.ldc + ccol + n;
         if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
         else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
@@ -531,6 +534,7 @@ __global__ void __launch_bounds__(256) fq3s_gemv_kernel(const SeqGemm g) {
       if (g.flags & FQ3C_GELU) v = gelu_f(v);
       if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
       if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+      if (g.flags & FQ3C_RELU2) { v = fmaxf(v, 0.f); v *= v; }
       const size_t ci = (size_t)m * g.ldc + ccol + n;
       if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
       else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
@@ -598,6 +602,7 @@ __global__ void __launch_bounds__(256) fq3s_ggemv_kernel(const SeqGemm g) {
     if (g.flags & FQ3C_GELU) v = gelu_f(v);
     if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
     if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+    if (g.flags & FQ3C_RELU2) { v = fmaxf(v, 0.f); v *= v; }
     const size_t ci = (size_t)p * g.ldc + n;
     if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
     else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
@@ -644,7 +649,7 @@ __global__ void __launch_bounds__(256) fq3s_tconv_kernel(const fq3c_op o) {
   else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(a);
 }
 
-// grid (M, groups); one block per (row, group).  An optional silu gate (p1, pitch i1) multiplies the row before the statistics
+// grid (M, groups); one block per (row, group).  FQ3C_CENTER: mean and variance instead of the mean square.  An optional silu gate (p1, pitch i1) multiplies the row before the statistics
 // (FQ3C_GATE_PRE) or the finished row (FQ3C_GATE_POST); weights repeat with period i2 when i2 > 0.
 __global__ void __launch_bounds__(128) fq3s_gnorm_kernel(const fq3c_op o) {
   __shared__ float red[32];
@@ -652,10 +657,21 @@ __global__ void __launch_bounds__(128) fq3s_gnorm_kernel(const fq3c_op o) {
   const float* x = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda + c0;
   const bool pre = (o.flags & FQ3C_GATE_PRE) != 0, post = (o.flags & FQ3C_GATE_POST) != 0;
   const float* gate = (pre || post) ? reinterpret_cast<const float*>(o.p1) + (size_t)m * o.i1 + c0 : nullptr;
+  float mean = 0.f;
+  if (o.flags & FQ3C_CENTER) {      // layer norm: the mean first, then the squared deviations from it (two passes, no cancellation)
+    float sm = 0.f;
+    for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
+      float v = x[i];
+      if (pre) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
+      sm += v;
+    }
+    mean = seq_block_sum(sm, red) / (float)gsz;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
     float v = x[i];
     if (pre) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
+    v -= mean;
     ss = fmaf(v, v, ss);
   }
   ss = seq_block_sum(ss, red);
@@ -666,7 +682,8 @@ __global__ void __launch_bounds__(128) fq3s_gnorm_kernel(const fq3c_op o) {
   for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
     float v = x[i];
     if (pre) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
-    v = v * rs * w[(c0 + i) % wmod];
+    v = (v - mean) * rs;
+    if (w) v *= w[(c0 + i) % wmod];
     if (post) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
     if (o.flags & FQ3C_RESID) v += reinterpret_cast<const float*>(o.res)[(size_t)m * o.ldr + c0 + i];
     if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[orow * o.ldc + c0 + i] = v;
@@ -881,6 +898,7 @@ __global__ void __launch_bounds__(256) fq3s_moe_combine_kernel(const fq3c_op o) 
   const float* Y = reinterpret_cast<const float*>(o.A);
   const float* x = reinterpret_cast<const float*>(o.B) + (size_t)m * o.ldr;
   const float* sh = o.res ? reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr : nullptr;
+  const float sg = (sh && o.scale) ? sigmoid_f(reinterpret_cast<const float*>(o.scale)[(size_t)m * o.i2]) : 1.f;   // one gate per token
   float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc;
   for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
     float acc = 0.f;
@@ -888,7 +906,7 @@ __global__ void __launch_bounds__(256) fq3s_moe_combine_kernel(const fq3c_op o) 
       const float v = ids[j] >= o.i1 ? x[i] : Y[(size_t)pos[j] * o.lda + i];
       acc = w ? fmaf(w[j], v, acc) : acc + v;
     }
-    if (sh) acc += sh[i];
+    if (sh) acc = fmaf(sg, sh[i], acc);
     c[i] = acc;
   }
 }
@@ -1325,15 +1343,17 @@ __global__ void __launch_bounds__(256) fq3s_rot_append_kernel(const fq3c_op o) {
     }
     float* qd = isq ? row + (size_t)hh * d : nullptr;
     TC* kd = isq ? nullptr : kc + (size_t)(hh - H) * d;
+    const bool halves = (o.flags & FQ3C_ROT_HALF) != 0;      // pairs (i, i + half) instead of (2i, 2i + 1)
     for (int i = lane; i < half; i += 32) {
       float sn, cs;
       sincosf(fp * freq[i], &sn, &cs);
       sn *= amp; cs *= amp;
-      float a = src[2 * i], b = src[2 * i + 1];
-      if (nw) { a = a * rs * nw[2 * i]; b = b * rs * nw[2 * i + 1]; }
+      const int ia = halves ? i : 2 * i, ib = halves ? i + half : 2 * i + 1;
+      float a = src[ia], b = src[ib];
+      if (nw) { a = a * rs * nw[ia]; b = b * rs * nw[ib]; }
       const float x = a * cs - b * sn, y = b * cs + a * sn;
-      if (isq) { qd[2 * i] = x; qd[2 * i + 1] = y; }
-      else { stf(kd + 2 * i, x); stf(kd + 2 * i + 1, y); }
+      if (isq) { qd[ia] = x; qd[ib] = y; }
+      else { stf(kd + ia, x); stf(kd + ib, y); }
     }
     if (isq && !nw) continue;     // the rest of a query head stays as it is
     for (int c = 2 * half + lane; c < d; c += 32) {
@@ -1787,13 +1807,22 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
 // product plus three shuffles per reduction; tokens arrive in rounds staged through shared memory.
 // ws row m (padded to a multiple of four floats): [unit q [G * dk] | unit k [G * dk] |] c1[H] | c2[H] [| q.k [G]]  (bracketed parts: delta
 // rule only; delta rule: c1 = decay, c2 = write strength; scan: c1 = decay, c2 = dt)
+// Two more modes share the walk.  Mode 2 (a decay per key channel and token): ws row m = alpha [H * dk], staged beside the token's
+// key and query as a third vector.  Mode 3 (one fixed decay per head): no per-token coefficients at all, hence no first launch.
 // ---------------------------------------------------------------------------------------------------------------------------
 __host__ __device__ inline int mstate_ws_cols(int H, int G, int dk, bool delta) { return ((delta ? 2 * G * dk + G : 0) + 2 * H + 3) & ~3; }
+__host__ __device__ inline int mstate_decay_cols(int H, int dk) { return (H * dk + 3) & ~3; }
 __host__ __device__ inline int mstate_ws_coef(int G, int dk, bool delta) { return delta ? 2 * G * dk : 0; }      // column of c1
 
 // grid (M), 128 threads
 __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) {
   const int m = blockIdx.x, H = o.i0, G = o.i1, dk = o.i2;
+  if (o.taps == 2) {     // alpha = sigmoid(z)^f1, through its logarithm -f1 softplus(-z): no underflow of the sigmoid on the way
+    float* a = reinterpret_cast<float*>(o.ws) + (size_t)m * mstate_decay_cols(H, dk);
+    const float* z = reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr + o.col_mod;
+    for (int c = threadIdx.x; c < H * dk; c += blockDim.x) a[c] = expf(-o.f1 * softplus_f(-z[c]));
+    return;
+  }
   const bool delta = o.taps == 0;
   float* w = reinterpret_cast<float*>(o.ws) + (size_t)m * mstate_ws_cols(H, G, dk, delta);
   float* cf = w + mstate_ws_coef(G, dk, delta);
@@ -1836,24 +1865,25 @@ constexpr int MS_COLS = 16;   // state columns per block (eight lanes each)
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
-// floats per staging buffer: (k, q) or (B, C) [MS_CH][2][8 slices of RPT + 4] | v [MS_CH][MS_COLS] | coefficients [MS_CH][4]
-__host__ __device__ constexpr int mstate_buf_floats(int rpt) { return MS_CH * 2 * 8 * (rpt + 4) + MS_CH * MS_COLS + MS_CH * 4; }
+// floats per staging buffer: (k, q) or (B, C) (and the decays) [MS_CH][NV][8 slices of RPT + 4] | v [MS_CH][MS_COLS] | coefficients [MS_CH][4]
+__host__ __device__ constexpr int mstate_buf_floats(int rpt, int nv = 2) { return MS_CH * nv * 8 * (rpt + 4) + MS_CH * MS_COLS + MS_CH * 4; }
 // grid (ceil(dv / 16), H), 128 threads: thread = (column tid / 8 of the tile, lane-of-eight tid % 8).  A lane holds RPT consecutive
 // rows of its state column (RPT * 8 >= dk; rows beyond dk stay zero: their key / query entries are zero padding), reads its slice
 // of the token's key and query with 16-byte shared-memory loads (slices are padded apart by four floats: no bank conflicts),
 // and a product is finished by three shuffles.  The next round's tokens arrive by cp.async while the current round is walked.
-template <int RPT>
+// NV = 3 (mode 2): a third staged vector per token, the decays of the head's key channels.
+template <int RPT, int NV = 2>
 __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) {
   extern __shared__ __align__(16) float msm[];
   constexpr int SL = RPT + 4, ROW = 8 * SL;
   const int H = o.i0, G = o.i1, dk = o.i2, dv = o.cin, h = blockIdx.y, g = h / (H / G);
-  const bool delta = o.taps == 0;
-  const int wc = mstate_ws_cols(H, G, dk, delta);
+  const bool delta = o.taps == 0, fixed = o.taps == 3;
+  const int wc = NV == 3 ? mstate_decay_cols(H, dk) : mstate_ws_cols(H, G, dk, delta);
   const int tid = threadIdx.x, sub = tid & 7, cl = tid >> 3, col = blockIdx.x * MS_COLS + cl;
   const bool live = col < dv;
-  constexpr int per = mstate_buf_floats(RPT);
+  constexpr int per = mstate_buf_floats(RPT, NV);
   {   // the padding between and behind the slices stays zero for the whole launch (only the token rows that will be used)
-    const int used = min(o.M, MS_CH) * 2 * ROW;
+    const int used = min(o.M, MS_CH) * NV * ROW;
     for (int i = tid; i < 2 * used; i += 128) msm[(i < used ? 0 : per - used) + i] = 0.f;
   }
   float S[RPT];
@@ -1863,33 +1893,38 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const float D = (!delta && o.B) ? reinterpret_cast<const float*>(o.B)[h] : 0.f;
   const float* wsb = reinterpret_cast<const float*>(o.ws);
   const float* rows = reinterpret_cast<const float*>(o.A);
-  const int vcol = (delta ? o.a_rows : 0) + h * dv;
+  const bool qkv_rows = delta || NV == 3 || fixed;       // layout (q | k | v) of the delta rule: queries at column 0, values at a_rows
+  const int vcol = (qkv_rows ? o.a_rows : 0) + h * dv;
   __syncthreads();
   // keys then queries (B then C) of this head's group, as columns of the rows they are staged from
   const float* vsrc = delta ? wsb : rows;
-  const int vstride = delta ? wc : o.lda, off0 = (delta ? G * dk : o.K) + g * dk, off1 = (delta ? 0 : o.a_rows) + g * dk;
+  const int vstride = delta ? wc : o.lda, off0 = (delta ? G * dk : o.K) + g * dk, off1 = ((delta || qkv_rows) ? 0 : o.a_rows) + g * dk;
   const int cfo = mstate_ws_coef(G, dk, delta);
-  const bool vec = dk % 4 == 0 && vstride % 4 == 0 && off0 % 4 == 0 && off1 % 4 == 0 && !(reinterpret_cast<uintptr_t>(vsrc) & 15);
+  const bool vec = dk % 4 == 0 && vstride % 4 == 0 && off0 % 4 == 0 && off1 % 4 == 0 && !(reinterpret_cast<uintptr_t>(vsrc) & 15) &&
+                   (NV < 3 || (wc % 4 == 0 && !(reinterpret_cast<uintptr_t>(wsb) & 15)));
+  const float fixed_c1 = fixed ? reinterpret_cast<const float*>(o.scale)[h] : 0.f;
   auto fetch = [&](const int t0, float* buf) {
     const int nt = min(MS_CH, o.M - t0);
     float* kq = buf;
-    float* vs = kq + MS_CH * 2 * ROW;
+    float* vs = kq + MS_CH * NV * ROW;
     float* cf = vs + MS_CH * MS_COLS;
     if (vec) {        // 16-byte copies: four consecutive entries never straddle a lane's slice (RPT is a multiple of four)
       const int n4 = dk >> 2;
       for (int idx = tid; idx < nt * n4; idx += 128) {
         const int tt = idx / n4, c = (idx - tt * n4) * 4, at = (c / RPT) * SL + (c % RPT);
         const float* sr = vsrc + (size_t)(t0 + tt) * vstride;
-        cp_async16(kq + tt * 2 * ROW + at, sr + off0 + c, true);
-        cp_async16(kq + tt * 2 * ROW + ROW + at, sr + off1 + c, true);
+        cp_async16(kq + tt * NV * ROW + at, sr + off0 + c, true);
+        cp_async16(kq + tt * NV * ROW + ROW + at, sr + off1 + c, true);
+        if (NV == 3) cp_async16(kq + tt * NV * ROW + 2 * ROW + at, wsb + (size_t)(t0 + tt) * wc + h * dk + c, true);
       }
     } else {
       for (int tt = 0; tt < nt; ++tt) {
         const float* sr = vsrc + (size_t)(t0 + tt) * vstride;
         for (int c = tid; c < dk; c += 128) {
           const int at = (c / RPT) * SL + (c % RPT);
-          cp_async4(kq + tt * 2 * ROW + at, sr + off0 + c);
-          cp_async4(kq + tt * 2 * ROW + ROW + at, sr + off1 + c);
+          cp_async4(kq + tt * NV * ROW + at, sr + off0 + c);
+          cp_async4(kq + tt * NV * ROW + ROW + at, sr + off1 + c);
+          if (NV == 3) cp_async4(kq + tt * NV * ROW + 2 * ROW + at, wsb + (size_t)(t0 + tt) * wc + h * dk + c);
         }
       }
     }
@@ -1897,12 +1932,13 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
       const int tt = idx / MS_COLS, c = blockIdx.x * MS_COLS + (idx % MS_COLS);
       if (c < dv) cp_async4(vs + idx, rows + (size_t)(t0 + tt) * o.lda + vcol + c);
     }
-    for (int idx = tid; idx < nt * 3; idx += 128) {
-      const int tt = idx / 3, which = idx - tt * 3;
-      const float* sr = wsb + (size_t)(t0 + tt) * wc + cfo;
-      if (which < 2) cp_async4(cf + tt * 4 + which, sr + which * H + h);
-      else if (delta) cp_async4(cf + tt * 4 + 2, sr + 2 * H + g);
-    }
+    if (NV < 3 && !fixed)
+      for (int idx = tid; idx < nt * 3; idx += 128) {
+        const int tt = idx / 3, which = idx - tt * 3;
+        const float* sr = wsb + (size_t)(t0 + tt) * wc + cfo;
+        if (which < 2) cp_async4(cf + tt * 4 + which, sr + which * H + h);
+        else if (delta) cp_async4(cf + tt * 4 + 2, sr + 2 * H + g);
+      }
     cp_async_commit();
   };
   fetch(0, msm);
@@ -1917,13 +1953,31 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
     }
     __syncthreads();
     const float* kq = msm + (it & 1) * per;
-    const float* vs = kq + MS_CH * 2 * ROW;
+    const float* vs = kq + MS_CH * NV * ROW;
     const float* cf = vs + MS_CH * MS_COLS;
     for (int tt = 0; tt < nt; ++tt) {
-      const float4* k4 = reinterpret_cast<const float4*>(kq + tt * 2 * ROW + sub * SL);
-      const float4* q4 = reinterpret_cast<const float4*>(kq + tt * 2 * ROW + ROW + sub * SL);
-      const float c1 = cf[tt * 4], c2 = cf[tt * 4 + 1], v = vs[tt * MS_COLS + cl];
+      const float4* k4 = reinterpret_cast<const float4*>(kq + tt * NV * ROW + sub * SL);
+      const float4* q4 = reinterpret_cast<const float4*>(kq + tt * NV * ROW + ROW + sub * SL);
+      const float v = vs[tt * MS_COLS + cl];
       float os[4] = {0.f, 0.f, 0.f, 0.f};       // four chains, so that a product's sum is not one long dependent row of multiply-adds
+      if (NV == 3) {      // S <- diag(alpha) S + k v^T, o = f0 S^T q
+        const float4* a4 = reinterpret_cast<const float4*>(kq + tt * NV * ROW + 2 * ROW + sub * SL);
+#pragma unroll
+        for (int r = 0; r < RPT / 4; ++r) {
+          const float4 kv = k4[r], qv = q4[r], av = a4[r];
+          S[4 * r] = fmaf(av.x, S[4 * r], kv.x * v); S[4 * r + 1] = fmaf(av.y, S[4 * r + 1], kv.y * v);
+          S[4 * r + 2] = fmaf(av.z, S[4 * r + 2], kv.z * v); S[4 * r + 3] = fmaf(av.w, S[4 * r + 3], kv.w * v);
+          os[0] = fmaf(qv.x, S[4 * r], os[0]); os[1] = fmaf(qv.y, S[4 * r + 1], os[1]);
+          os[2] = fmaf(qv.z, S[4 * r + 2], os[2]); os[3] = fmaf(qv.w, S[4 * r + 3], os[3]);
+        }
+        float ot = (os[0] + os[1]) + (os[2] + os[3]);
+        ot += __shfl_xor_sync(0xffffffffu, ot, 1);
+        ot += __shfl_xor_sync(0xffffffffu, ot, 2);
+        ot += __shfl_xor_sync(0xffffffffu, ot, 4);
+        if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = ot * o.f0;
+        continue;
+      }
+      const float c1 = fixed ? fixed_c1 : cf[tt * 4], c2 = fixed ? o.f0 : cf[tt * 4 + 1];
       if (delta) {
         // both products with the stored state in one pass and one round of shuffles: with S' = c1 S + k u^T,
         // S'^T q = c1 S^T q + u (k . q), and u = c2 (v - c1 S^T k); k . q comes with the token
@@ -2045,4 +2099,41 @@ __global__ void __launch_bounds__(256) fq3s_glu_kernel(const fq3c_op o) {
   const float v = g / (1.f + expf(-g)) * u;
   if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)r * o.ldc + c] = v;
   else reinterpret_cast<bf16*>(o.C)[(size_t)r * o.ldc + c] = __float2bfloat16_rn(v);
+}
+
+// ===========================================================================================================================
+// ABI 9 (kind 32): the residual sum of a layer whose sublayers run side by side on one normed input, fused with the norm that
+// reads the finished stream (a layer norm without bias, or an RMS norm).
+// ===========================================================================================================================
+// grid (M), 256 threads, dynamic shared memory N floats (the finished row).  Pass 1 forms the weighted sum of the slices, writes it
+// and keeps it; passes 2 and 3 take the mean and the mean squared deviation from the kept row; pass 4 writes the normed row.
+// A thread only ever reads back entries it wrote itself, and C may be slice 0 (every entry is read before it is written).
+__global__ void __launch_bounds__(256) fq3s_sum_norm_kernel(const fq3c_op o) {
+  extern __shared__ float snm[];
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const float* a = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
+  const float* w = reinterpret_cast<const float*>(o.p0);
+  float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc;
+  float sm = 0.f;
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
+    float v = 0.f;
+    for (int j = 0; j < o.i0; ++j) v = fmaf(w[j], a[(size_t)j * (size_t)o.K + i], v);
+    c[i] = v;
+    if (o.C2) reinterpret_cast<bf16*>(o.C2)[(size_t)m * o.ldc + i] = __float2bfloat16_rn(v);
+    snm[i] = v;
+    sm += v;
+  }
+  if (!o.norm_out) return;
+  float mean = 0.f;
+  if (o.flags & FQ3C_CENTER) mean = seq_block_sum(sm, red) / (float)o.N;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) { const float d = snm[i] - mean; ss = fmaf(d, d, ss); }
+  const float rs = 1.f / sqrtf(seq_block_sum(ss, red) / (float)o.N + o.norm_eps);
+  const float* nw = reinterpret_cast<const float*>(o.norm_w);
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
+    const float n = (snm[i] - mean) * rs * nw[i];
+    if (o.flags & FQ3C_F32) reinterpret_cast<float*>(o.norm_out)[(size_t)m * o.norm_ld + i] = n;
+    else reinterpret_cast<bf16*>(o.norm_out)[(size_t)m * o.norm_ld + i] = __float2bfloat16_rn(n);
+  }
 }

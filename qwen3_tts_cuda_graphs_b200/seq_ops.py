@@ -1,4 +1,4 @@
-"""Mechanisms of the sequence models as op-list fragments (include/fq3_codec.h, kinds 12-31).
+"""Mechanisms of the sequence models as op-list fragments (include/fq3_codec.h, kinds 12-32).
 
 A `StepBuilder` lowers ONE step (M new tokens of the request in one slot) to a flat list of `fq3c_op` records over buffers
 it allocates; the list is handed to `fq3c_run` / replayed as a CUDA graph like the codec's plans.  Each mechanism is a method
@@ -13,7 +13,9 @@ with its constants as arguments, so another design composes them differently:
   (key / value cache, grouped heads, partial rotary, per-head query / key norms, score cap, window with kept first positions,
   chunked mask, distance penalty, sink, output gate, borrowed cache), rglru (gated diagonal linear recurrence block), delta_rule and state_space (matrix state per
   head), polynorm_ff, xielu_ff, moe_ff (softmax or sigmoid router with correction, neighbour groups, identity experts, shared
-  expert; gelu or gated experts; weights on the experts' outputs or inputs).
+  expert; gelu, relu^2 or gated experts; weights on the experts' outputs or inputs; router bias; gated shared expert), sum_norm (the
+  weighted residual sum of sublayers that ran side by side, chained into the next layer norm or RMS norm), channel_decay_attention
+  and retention (linear attentions on the matrix-state scan: a decay per key channel and token, one fixed decay per head).
 
 Precision: `f32=True` runs every product in true 32-bit.  Otherwise weights and product operands are bf16 with f32
 accumulation; the residual stream, norms, softmax, router, recurrence and everything entering it are f32 in both modes.
@@ -24,10 +26,12 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .codec import (F_A_F32, F_BIAS, F_SWIGLU, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RAW_WEIGHTS, F_RESID, F_SIGMOID, F_SILU,
+from .codec import (F_A_F32, F_BIAS, F_CENTER, F_SWIGLU, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RAW_WEIGHTS, F_RELU2, F_RESID,
+                    F_ROT_HALF, F_SIGMOID, F_SILU,
                     K_BDGEMM, K_CACHE_ATTN, K_COMMIT, K_DEPTH_MIX, K_DYT, K_EMBED, K_GEMM, K_GGEMM, K_GLU, K_GNORM, K_HYPER, K_LATENT_ATTN,
-                    K_LRU_SCAN, K_MOE_COMBINE, K_MOE_SORT, K_MSTATE_SCAN, K_POLYNORM, K_ROT_APPEND, K_ROUTER, K_TCONV, K_XIELU, Op, _Plan)
-from .config import DeltaRuleConfig, LatentAttentionConfig, MoEFFConfig, RglruConfig, SoftmaxAttentionConfig, StateSpaceConfig
+                    K_LRU_SCAN, K_MOE_COMBINE, K_MOE_SORT, K_MSTATE_SCAN, K_POLYNORM, K_ROT_APPEND, K_ROUTER, K_SUM_NORM, K_TCONV, K_XIELU, Op, _Plan)
+from .config import (ChannelDecayAttentionConfig, DeltaRuleConfig, LatentAttentionConfig, MoEFFConfig, RetentionConfig, RglruConfig,
+                     SoftmaxAttentionConfig, StateSpaceConfig)
 from .seq_state import SlotState
 
 
@@ -114,15 +118,18 @@ class StepBuilder:
         self._op(K_TCONV, **kw)
         return out
 
-    def group_norm(self, x: torch.Tensor, w: torch.Tensor, groups: int, eps: float, out: torch.Tensor, n: Optional[int] = None,
+    def group_norm(self, x: torch.Tensor, w: Optional[torch.Tensor], groups: int, eps: float, out: torch.Tensor, n: Optional[int] = None,
                    col: int = 0, residual: Optional[torch.Tensor] = None, out_bf16: Optional[torch.Tensor] = None,
                    append_at_position: bool = False, gate: Optional[torch.Tensor] = None, gate_col: int = 0, gate_first: bool = False,
-                   weight_period: int = 0):
+                   weight_period: int = 0, center: bool = False, rows: Optional[int] = None):
         """out = (residual +) rms_unit_per_group(x) * w.  `gate` (f32 rows, columns from gate_col): the row times silu(gate) before the
-        statistics (gate_first) or after the weights.  weight_period > 0: w has that many entries and repeats (a per-head norm)."""
+        statistics (gate_first) or after the weights.  weight_period > 0: w has that many entries and repeats (a per-head norm).
+        w None: no weights (n required).  center: the statistics are mean and variance (a layer norm without bias)."""
         n = n or w.shape[0]
-        kw = dict(M=self.M, N=n, i0=groups, f0=eps, A=_ptr(x, col), lda=x.shape[1], scale=w, C=out, ldc=out.shape[1], i2=weight_period,
-                  flags=self._oflag(out) | (F_RESID if residual is not None else 0))
+        kw = dict(M=rows or self.M, N=n, i0=groups, f0=eps, A=_ptr(x, col), lda=x.shape[1], C=out, ldc=out.shape[1], i2=weight_period,
+                  flags=self._oflag(out) | (F_RESID if residual is not None else 0) | (F_CENTER if center else 0))
+        if w is not None:
+            kw["scale"] = w
         if gate is not None:
             kw["p1"], kw["i1"] = _ptr(gate, gate_col), gate.shape[1]
             kw["flags"] |= F_GATE_PRE if gate_first else F_GATE_POST
@@ -138,14 +145,15 @@ class StepBuilder:
         return out
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
-               rows: Optional[int] = None, force_f32: bool = False, glu: bool = False):
-        """out = act(x W^T + bias).  x and W share a type (bf16, or f32 for true 32-bit: `force_f32` for a router).  glu: W's rows
+               rows: Optional[int] = None, force_f32: bool = False, glu: bool = False, relu2: bool = False):
+        """out = act(x W^T + bias), act = gelu, max(., 0)^2 (relu2) or none.  x and W share a type (bf16, or f32 for true 32-bit:
+        `force_f32` for a router).  glu: W's rows
         alternate (gate_n, up_n) and out [M, N / 2] = silu(gate) * up, formed in the product's epilogue."""
         M = rows or self.M
         N, K = w.shape
         f32 = w.dtype == torch.float32
         assert x.dtype == w.dtype, (x.dtype, w.dtype)
-        flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_GELU if gelu else 0) | (F_F32 if f32 else 0)
+        flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_GELU if gelu else 0) | (F_F32 if f32 else 0) | (F_RELU2 if relu2 else 0)
         if out.dtype == torch.float32 or M <= 4 or glu:
             flags |= F_NOROUND      # f32 results stay unrounded; with a few rows the flag also picks the weight-streaming product
         if glu:
@@ -267,6 +275,21 @@ class StepBuilder:
         self._op(K_DEPTH_MIX, **kw)
         return out
 
+    def sum_norm(self, parts: torch.Tensor, count: int, weights: torch.Tensor, norm_w: Optional[torch.Tensor] = None,
+                 norm_out: Optional[torch.Tensor] = None, eps: float = 0.0, center: bool = False, out: Optional[torch.Tensor] = None):
+        """parts f32 [slices, M, N]: out (default parts[0], the residual stream, in place) = sum_(j < count) weights[j] * parts[j],
+        weights f32 [count] on the device.  With norm_out: also norm_out = norm(out) * norm_w — RMS, or with `center` mean / variance —
+        in the same launch (the norm that reads the finished stream next)."""
+        out = parts[0] if out is None else out
+        kw = dict(M=self.M, N=parts.shape[2], i0=count, K=parts.shape[1] * parts.shape[2], A=parts, lda=parts.shape[2], p0=weights, C=out,
+                  ldc=out.shape[1], flags=F_OUT_F32 | (F_CENTER if center else 0))
+        if norm_out is not None:
+            kw.update(norm_out=norm_out, norm_w=norm_w, norm_ld=norm_out.shape[1], norm_eps=float(eps))
+            if norm_out.dtype == torch.float32:
+                kw["flags"] |= F_F32
+        self._op(K_SUM_NORM, **kw)
+        return out
+
     # ---- softmax attention over a key / value cache ---------------------------------------------------
     def softmax_attention(self, h: torch.Tensor, c: SoftmaxAttentionConfig, w: dict, kcache: str, vcache: str, out: torch.Tensor,
                           eps: float = 1e-6):
@@ -356,6 +379,39 @@ class StepBuilder:
         yn = self.group_norm(y, w["norm"], c.norm_groups, eps, self.buf("ss.yn", M, inner, self.adt), gate=raw, gate_col=0, gate_first=True)
         return self.linear(yn, w["o"], out)
 
+    def channel_decay_attention(self, h: torch.Tensor, c: ChannelDecayAttentionConfig, w: dict, state: str, eps: float, out: torch.Tensor):
+        """h [M, width] -> out f32 [M, width].  w: win [2 H dim + 2 H vdim + rank, width] (q | k | v | output gate | decay latent),
+        a2 [1, H dim, rank] and a2_b f32 [H dim] (the decay input's up-projection, run on the f32 latent), norm f32 [vdim],
+        o [width, H vdim].  Per head S <- diag(alpha) S + k v^T, alpha = sigmoid(z)^(1/tau), read out by q dim^(-1/2)."""
+        M, H, d, dv = self.M, c.heads, c.dim, c.vdim
+        gcol = 2 * H * d + H * dv
+        acol = gcol + H * dv
+        raw = self.linear(h, w["win"], self.buf("cd.raw", M, w["win"].shape[0]))
+        z = self.block_linear(raw, w["a2"], self.buf("cd.z", M, H * d), bias=w["a2_b"], exact=True, col=acol)
+        y = self.buf("cd.y", M, H * dv)
+        ws = self.buf("cd.ws", M, -(-(H * d) // 4) * 4)
+        self._op(K_MSTATE_SCAN, M=M, N=H * dv, taps=2, i0=H, i1=H, i2=d, cin=dv, K=H * d, a_rows=2 * H * d, A=raw, lda=raw.shape[1],
+                 res=z, ldr=z.shape[1], col_mod=0, f0=float(d) ** -0.5, f1=1.0 / float(c.tau), p0=self.slot.cur[state], C2=self.slot.next[state],
+                 C=y, ldc=y.shape[1], ws=ws, ws_bytes=ws.numel() * 4, flags=F_OUT_F32)
+        yn = self.group_norm(y, w["norm"], H, eps, self.buf("cd.yn", M, H * dv, self.adt), n=H * dv, gate=raw, gate_col=gcol, weight_period=dv)
+        return self.linear(yn, w["o"], out)
+
+    def retention(self, h: torch.Tensor, c: RetentionConfig, w: dict, state: str, eps: float, out: torch.Tensor):
+        """h [M, width] -> out f32 [M, width].  w: win [2 H dim + 2 H vdim, width] (q | k | v | output gate), decay f32 [H],
+        freq f32 [rot_dims / 2] or None, o [width, H vdim].  q and k turn in place (pairs i, i + rot_dims / 2); per head
+        S <- decay S + (k dim^(-1/2)) v^T, o = S^T q; the read-out is divided by its root mean square per head (no weights)."""
+        M, H, d, dv = self.M, c.heads, c.dim, c.vdim
+        gcol = 2 * H * d + H * dv
+        raw = self.linear(h, w["win"], self.buf("rt.raw", M, w["win"].shape[0]))
+        if c.rot_dims > 0:      # 2 H heads (queries, then keys) turn where they lie; nothing is appended
+            self._op(K_ROT_APPEND, M=M, i0=2 * H, i1=0, i2=d, cin=0, taps=c.rot_dims, K=0, a_rows=0, A=raw, lda=raw.shape[1], B=w["freq"],
+                     p0=self.slot.pos, flags=F_ROT_HALF)
+        y = self.buf("rt.y", M, H * dv)
+        self._op(K_MSTATE_SCAN, M=M, N=H * dv, taps=3, i0=H, i1=H, i2=d, cin=dv, K=H * d, a_rows=2 * H * d, A=raw, lda=raw.shape[1],
+                 scale=w["decay"], f0=float(d) ** -0.5, p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1], flags=F_OUT_F32)
+        yn = self.group_norm(y, None, H, eps, self.buf("rt.yn", M, H * dv, self.adt), n=H * dv, gate=raw, gate_col=gcol)
+        return self.linear(yn, w["o"], out)
+
     def xielu_ff(self, x: torch.Tensor, w: dict, out: torch.Tensor):
         """out f32 = W_down xielu(W_up x); w: up [ff, width], down [width, ff], act f32 [2]."""
         ff = w["up"].shape[0]
@@ -379,13 +435,18 @@ class StepBuilder:
         silu(gate) * up is formed in the products' epilogues, and with c.weight_input the choice's weight multiplies both (the
         expert's input) instead of the expert's output.  The router's logits are f32 either way:
         f32 router weights take the f32 rows (true 32-bit product); bf16 ones take the bf16 rows, whose products with the weights
-        are exact in f32 and are summed in f32."""
+        are exact in f32 and are summed in f32.  c.act == "relu2": max(., 0)^2 instead of gelu.  c.router_bias: router_b f32 added
+        to the logits.  c.shared_gate: the router matrix carries one more row (and router_b one more entry, zero) whose product, through
+        a sigmoid, multiplies the shared expert's output."""
         M, n, top, E = self.M, c.routed, c.top, c.experts
         width = x32.shape[1]
-        z = self.linear(x32 if w["router"].dtype == torch.float32 else xop, w["router"], self.buf("moe.z", M, n))
+        zc = w["router"].shape[0]        # n, or n + 1 with the shared expert's gate row
+        assert zc == n + (1 if c.shared_gate else 0)
+        z = self.linear(x32 if w["router"].dtype == torch.float32 else xop, w["router"], self.buf("moe.z", M, zc),
+                        bias=w.get("router_b") if c.router_bias else None)
         ids = self.buf("moe.ids", M, top, torch.int32)
         wt = self.buf("moe.w", M, top)
-        kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=n, C=ids, C2=wt,
+        kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=zc, C=ids, C2=wt,
                   flags=(F_SIGMOID if c.score == "sigmoid" else 0) | (0 if c.renorm else F_RAW_WEIGHTS))
         if w.get("correction") is not None:
             kw["bias"] = w["correction"]
@@ -407,7 +468,7 @@ class StepBuilder:
         else:
             assert not c.weight_input
             self._op(K_GGEMM, M=M * top, N=ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=act, ldc=ff,
-                     flags=F_GELU | self._oflag(act) | (F_F32 if f32 else 0))
+                     flags=(F_RELU2 if c.act == "relu2" else F_GELU) | self._oflag(act) | (F_F32 if f32 else 0))
         y = self.buf("moe.y", M * top, width)
         self._op(K_GGEMM, M=M * top, N=width, K=ff, i0=E, A=act, lda=ff, B=w["down"], p0=seg, C=y, ldc=width,
                  flags=F_OUT_F32 | (F_F32 if f32 else 0))
@@ -416,13 +477,17 @@ class StepBuilder:
             sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0] // 2, self.adt), glu=True)
             sh = self.linear(sa, w["shared_down"], self.buf("moe.sh", M, width))
         elif w.get("shared_up") is not None:
-            sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0], self.adt), gelu=True)
+            sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0], self.adt), gelu=c.act != "relu2",
+                             relu2=c.act == "relu2")
             sh = self.linear(sa, w["shared_down"], self.buf("moe.sh", M, width))
         kw = dict(M=M, N=width, i0=top, i1=E, A=y, lda=width, B=x32, ldr=width, p0=ids, ws=pos, C=out, ldc=out.shape[1])
         if not c.weight_input:
             kw["p1"] = wt
         if sh is not None:
             kw["res"] = sh
+            if c.shared_gate:
+                kw["scale"], kw["i2"] = _ptr(z, n), zc
+                self.plan.keep.append(z)
         self._op(K_MOE_COMBINE, **kw)
         return out
 
