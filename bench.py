@@ -269,9 +269,9 @@ def main():
                     help="extra leg at N=1: this many requests through serving.BatchScheduler (16 concurrent); 0 = skip")
     ap.add_argument("--seq-model", action="store_true", dest="seq_model",
                     help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of the sequence "
-                         "models (Sidalorn, Redodra, Ratizen) at real-size layers beside the talker (qwen3_tts_cuda_graphs_b200/seq_bench.py); one GPU")
+                         "models (Sidalorn, Redodra, Ratizen, Zudusun) at real-size layers beside the talker (qwen3_tts_cuda_graphs_b200/seq_bench.py); one GPU")
     ap.add_argument("--seq-tokens", type=int, default=2048, dest="seq_tokens", help="--seq-model: prompt length / decode context")
-    ap.add_argument("--seq-sizes", default="w1024,w2048", dest="seq_sizes", help="--seq-model: comma list of sizes (w1024, w2048: Sidalorn; r1024, r2048: Redodra; z1024, z2048: Ratizen)")
+    ap.add_argument("--seq-sizes", default="w1024,w2048", dest="seq_sizes", help="--seq-model: comma list of sizes (w1024, w2048: Sidalorn; r1024, r2048: Redodra; z1024, z2048: Ratizen; u1024, u2048: Zudusun)")
     args = ap.parse_args()
     if args.seq_model:
         from qwen3_tts_cuda_graphs_b200 import seq_bench

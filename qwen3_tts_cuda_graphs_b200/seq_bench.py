@@ -1,7 +1,8 @@
 """Throughput of a sequence model at layer sizes that resemble a real model's, beside the closest model of the framework.
 
 `bench.py --seq-model` (the default workload of bench.py is untouched).  Random weights, synthetic tokens.  Sizes w* are Sidalorn
-models, r* Redodra models, z* Ratizen models (`--seq-sizes z1024,r1024,w1024` puts the designs side by side at equal width).  For
+models, r* Redodra models, z* Ratizen models, u* Zudusun models (`--seq-sizes u1024,z1024,r1024,w1024` puts the designs side by side at
+equal width).  For
 each size:
   * prefill: one step of T prompt tokens through `SequenceEngine.step` (tokens / s), and the same in portions;
   * decode: single-token steps at context T (tokens / s), replayed as CUDA graphs as the generation path does;
@@ -22,8 +23,9 @@ from collections import defaultdict
 import torch
 
 from . import codec as K
-from .config import (DeltaRuleConfig, DenseFFConfig, LatentAttentionConfig, MoEFFConfig, ParallelMixerConfig, RatizenConfig, RedodraConfig,
-                     RglruConfig, SeqLayerConfig, SidalornConfig, SoftmaxAttentionConfig, StateSpaceConfig)
+from .config import (ChannelDecayAttentionConfig, DeltaRuleConfig, DenseFFConfig, LatentAttentionConfig, MoEFFConfig, ParallelMixerConfig,
+                     RatizenConfig, RedodraConfig, RetentionConfig, RglruConfig, ScaledPairMixerConfig, SeqLayerConfig, SidalornConfig,
+                     SoftmaxAttentionConfig, StateSpaceConfig, ZudusunConfig)
 
 KIND_NAMES = {K.K_GEMM: "gemm (tcgen05 / gemv)", K.K_RMSNORM: "rmsnorm", K.K_ATTN: "attention (prefill, CUDA cores)", 8: "qk-norm + rope + kv",
               K.K_EMBED: "embed / gather", K.K_TCONV: "time conv", K.K_GNORM: "group norm", K.K_BDGEMM: "block-diagonal product",
@@ -31,7 +33,7 @@ KIND_NAMES = {K.K_GEMM: "gemm (tcgen05 / gemv)", K.K_RMSNORM: "rmsnorm", K.K_ATT
               K.K_MOE_SORT: "moe sort", K.K_GGEMM: "grouped expert product", K.K_MOE_COMBINE: "moe combine", K.K_COMMIT: "state commit",
               K.K_DYT: "dynamic-tanh norm", K.K_DEPTH_MIX: "depth mix", K.K_XIELU: "xielu", K.K_ROT_APPEND: "rotary + cache append",
               K.K_CACHE_ATTN: "cached softmax attention", K.K_MSTATE_SCAN: "matrix-state scan", K.K_HYPER: "residual streams (+ norm)",
-              K.K_GLU: "gated unit"}
+              K.K_GLU: "gated unit", K.K_SUM_NORM: "residual sum (+ layer norm)"}
 
 
 def peaks():
@@ -78,7 +80,18 @@ def sizes():
         layers = tuple(SeqLayerConfig(t, att if t == "attention" else lat, moe) for t in order)
         return RatizenConfig(vocab, width, 1e-5, 2.0, 0.7, streams, True, 0.3, layers)
 
-    return {"z1024": ratizen(1024, 16, 4, 256, 384, 16, 2, 768, 1536, ("attention", "latent_attention", "latent_attention") * 2),
+    def zudusun(width, heads, kv, lin_heads, experts, top, expert_ff, shared_ff, order, window=1024, vocab=3072):
+        left = SoftmaxAttentionConfig(heads // 2, max(1, kv // 2), 128, 128, 128 ** -0.5)
+        right = ChannelDecayAttentionConfig(lin_heads, 64, 128, 16.0, 16)
+        att = SoftmaxAttentionConfig(heads, kv, 128, 128, 128 ** -0.5, rot_dims=64, rot_base=5e5, window=window, bias=True, qk_norm=True, zero_sink=True)
+        ret = RetentionConfig(lin_heads, 128, 128, tuple(1.0 - 2.0 ** (-5 - (8 * h) // lin_heads) for h in range(lin_heads)), rot_dims=128, rot_base=1e6)
+        mix = {"parallel": ScaledPairMixerConfig(left, right, 0.8, 0.5), "attention": att, "retention": ret}
+        moe = MoEFFConfig(experts, 0, top, 1, 1, 1.0, expert_ff, shared_ff, act="relu2", router_bias=True, shared_gate=True)
+        return ZudusunConfig(vocab, width, 1e-5, tuple(SeqLayerConfig(t, mix[t], moe) for t in order), tuple(range(len(order))))
+
+    return {"u1024": zudusun(1024, 16, 4, 8, 16, 2, 768, 1536, ("parallel", "attention", "retention") * 2),
+            "u2048": zudusun(2048, 32, 8, 16, 32, 4, 1024, 2048, ("parallel", "attention", "retention")),
+            "z1024": ratizen(1024, 16, 4, 256, 384, 16, 2, 768, 1536, ("attention", "latent_attention", "latent_attention") * 2),
             "z2048": ratizen(2048, 32, 8, 512, 768, 32, 4, 1024, 2048, ("attention", "latent_attention", "latent_attention")),
             "w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1),
             "r1024": redodra(1024, 16, 4, 512, 16, 64, 3072, ("delta", "attention", "parallel", "shared", "delta", "parallel")),
@@ -94,6 +107,10 @@ def random_model(cfg, device, seed=0):
         from .ratizen import RatizenModel, init_synthetic
 
         return RatizenModel(cfg, init_synthetic(cfg, seed).get, device, f32=False)
+    if isinstance(cfg, ZudusunConfig):
+        from .zudusun import ZudusunModel, init_synthetic
+
+        return ZudusunModel(cfg, init_synthetic(cfg, seed).get, device, f32=False)
     from .sidalorn import SidalornModel, tensor_specs
 
     g = torch.Generator(device=device).manual_seed(seed)
@@ -139,7 +156,10 @@ def op_cost(o, ctx_keys: float):
         return 2.0 * M * o.i0 * (o.i2 + o.cin) * keys, min(ctx_keys + M / 2, keys + M) * o.i1 * (o.i2 + o.cin) * ws + M * o.i0 * (o.i2 * 4 + o.cin * outs)
     if k == K.K_MSTATE_SCAN:
         per = 7.0 if o.taps == 0 else 5.0
-        return per * M * o.i0 * o.i2 * o.cin, M * (2 * o.i1 * o.i2 + 2 * o.i0 * o.cin) * 4 + 2 * o.i0 * o.i2 * o.cin * 4
+        vecs = 6 if o.taps == 2 else 2        # channel decays: their inputs are read, the decays written and read again beside q and k
+        return per * M * o.i0 * o.i2 * o.cin, M * (vecs * o.i1 * o.i2 + 2 * o.i0 * o.cin) * 4 + 2 * o.i0 * o.i2 * o.cin * 4
+    if k == K.K_SUM_NORM:
+        return 0.0, M * N * (4 * (o.i0 + 1) + ((4 if f32 else 2) if o.norm_out else 0))
     if k == K.K_ROT_APPEND:
         return 0.0, M * (o.i0 * o.i2 * 8 + o.i1 * (o.i2 + o.cin) * (4 + ws))
     if k == K.K_HYPER:
@@ -254,7 +274,7 @@ def bench_sequence_model(name, cfg, T, device):
         if isinstance(cfg, RedodraConfig):
             wb += operand_bytes(w)
             continue
-        if isinstance(cfg, RatizenConfig):
+        if isinstance(cfg, (RatizenConfig, ZudusunConfig)):
             wb += operand_bytes(w["mix"])
             f = w.get("ff")
             if f:
