@@ -164,8 +164,9 @@ enum fq3c_kind {
    *   FQ3C_GEMM / FQ3C_GGEMM: FQ3C_RELU2 epilogue max(z, 0)^2.
    *   FQ3C_MOE_COMBINE: scale (f32, pitch i2 floats per token), when given: res is multiplied by sigmoid(scale[m * i2]).
    *   FQ3C_MSTATE_SCAN: taps = 2 (linear attention with a decay per key channel and token): queries of head h at column h * i2,
-   *     keys at K + h * i2, values at a_rows + h * cin of the rows A; decay inputs z of head h at column col_mod + h * i2 of the rows
-   *     res; alpha = sigmoid(z)^f1 = exp(-f1 softplus(-z));  S <- diag(alpha) S + k v^T;  o = f0 S^T q;  i1 = i0;
+   *     keys at K + h * i2, values at a_rows + h * cin of the rows A; the decay latent (m_begin entries, f32) at column col_mod of the
+   *     rows res; z = B lat + bias with B [i0 * i2, m_begin] (bf16; FQ3C_F32: f32) and bias f32 [i0 * i2] or NULL, formed in the first
+   *     launch; alpha = sigmoid(z)^f1 = exp(-f1 softplus(-z));  S <- diag(alpha) S + k v^T;  o = f0 S^T q;  i1 = i0;
    *     ws = f32 [M, round_up(i0 * i2, 4)] (the decays).
    *     taps = 3 (retention: one fixed decay per head): same columns; S <- scale[h] S + (f0 k) v^T;  o = S^T q; no ws, no res.   */
 };

@@ -1303,7 +1303,8 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
         if (!o.res || !o.scale || !o.ws) return fail("mstate_scan: raw projections, A_log and a workspace required");
         if (o.ws_bytes < (int64_t)o.M * mstate_ws_cols(o.i0, o.i1, o.i2, o.taps == 0) * 4) return fail("mstate_scan: workspace too small");
       } else if (o.taps == 2) {
-        if (!o.res || !o.ws || o.i1 != o.i0) return fail("mstate_scan: channel decays need their inputs, a workspace and one key head per head");
+        if (!o.res || !o.ws || !o.B || o.i1 != o.i0 || o.m_begin < 1 || o.m_begin > MS_MAX_RANK)
+          return fail("mstate_scan: channel decays need their latent rows, the up-projection (inner size 1 .. 1024), a workspace and one key head per head");
         if (o.ws_bytes < (int64_t)o.M * mstate_decay_cols(o.i0, o.i2) * 4) return fail("mstate_scan: workspace too small");
       } else if (!o.scale || o.i1 != o.i0) {
         return fail("mstate_scan: fixed decays need one value and one key head per head");

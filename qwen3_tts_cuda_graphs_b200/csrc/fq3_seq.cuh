@@ -1814,13 +1814,32 @@ __host__ __device__ inline int mstate_ws_cols(int H, int G, int dk, bool delta) 
 __host__ __device__ inline int mstate_decay_cols(int H, int dk) { return (H * dk + 3) & ~3; }
 __host__ __device__ inline int mstate_ws_coef(int G, int dk, bool delta) { return delta ? 2 * G * dk : 0; }      // column of c1
 
+constexpr int MS_MAX_RANK = 1024;     // inner size of the decay projection (mode 2)
 // grid (M), 128 threads
 __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) {
   const int m = blockIdx.x, H = o.i0, G = o.i1, dk = o.i2;
-  if (o.taps == 2) {     // alpha = sigmoid(z)^f1, through its logarithm -f1 softplus(-z): no underflow of the sigmoid on the way
+  if (o.taps == 2) {
+    // z = U lat + b with the row's decay latent lat (m_begin entries of the raw rows, f32) and U = B [H * dk, m_begin] (bf16, F32: f32):
+    // the up-projection is a few multiply-adds per channel, done here instead of in a product launch of its own.
+    // alpha = sigmoid(z)^f1, through its logarithm -f1 softplus(-z): no underflow of the sigmoid on the way.
+    __shared__ float lat[MS_MAX_RANK];
+    const int R = o.m_begin;
+    const float* lr = reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr + o.col_mod;
+    for (int r = threadIdx.x; r < R; r += blockDim.x) lat[r] = lr[r];
+    __syncthreads();
     float* a = reinterpret_cast<float*>(o.ws) + (size_t)m * mstate_decay_cols(H, dk);
-    const float* z = reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr + o.col_mod;
-    for (int c = threadIdx.x; c < H * dk; c += blockDim.x) a[c] = expf(-o.f1 * softplus_f(-z[c]));
+    const float* zb = reinterpret_cast<const float*>(o.bias);
+    for (int c = threadIdx.x; c < H * dk; c += blockDim.x) {
+      float z = zb ? zb[c] : 0.f;
+      if (o.flags & FQ3C_F32) {
+        const float* u = reinterpret_cast<const float*>(o.B) + (size_t)c * R;
+        for (int r = 0; r < R; ++r) z = fmaf(lat[r], u[r], z);
+      } else {
+        const bf16* u = reinterpret_cast<const bf16*>(o.B) + (size_t)c * R;
+        for (int r = 0; r < R; ++r) z = fmaf(lat[r], __bfloat162float(u[r]), z);
+      }
+      a[c] = expf(-o.f1 * softplus_f(-z));
+    }
     return;
   }
   const bool delta = o.taps == 0;
@@ -1890,7 +1909,7 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const float* st = reinterpret_cast<const float*>(o.p0) + (size_t)h * dk * dv;
 #pragma unroll
   for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; S[r] = (live && i < dk) ? st[(size_t)i * dv + col] : 0.f; }
-  const float D = (!delta && o.B) ? reinterpret_cast<const float*>(o.B)[h] : 0.f;
+  const float D = (o.taps == 1 && o.B) ? reinterpret_cast<const float*>(o.B)[h] : 0.f;
   const float* wsb = reinterpret_cast<const float*>(o.ws);
   const float* rows = reinterpret_cast<const float*>(o.A);
   const bool qkv_rows = delta || NV == 3 || fixed;       // layout (q | k | v) of the delta rule: queries at column 0, values at a_rows

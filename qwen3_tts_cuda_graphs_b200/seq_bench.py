@@ -156,7 +156,7 @@ def op_cost(o, ctx_keys: float):
         return 2.0 * M * o.i0 * (o.i2 + o.cin) * keys, min(ctx_keys + M / 2, keys + M) * o.i1 * (o.i2 + o.cin) * ws + M * o.i0 * (o.i2 * 4 + o.cin * outs)
     if k == K.K_MSTATE_SCAN:
         per = 7.0 if o.taps == 0 else 5.0
-        vecs = 6 if o.taps == 2 else 2        # channel decays: their inputs are read, the decays written and read again beside q and k
+        vecs = 4 if o.taps == 2 else 2        # channel decays: written by the first launch and read again by the walk, beside q and k
         return per * M * o.i0 * o.i2 * o.cin, M * (vecs * o.i1 * o.i2 + 2 * o.i0 * o.cin) * 4 + 2 * o.i0 * o.i2 * o.cin * 4
     if k == K.K_SUM_NORM:
         return 0.0, M * N * (4 * (o.i0 + 1) + ((4 if f32 else 2) if o.norm_out else 0))

@@ -381,18 +381,20 @@ class StepBuilder:
 
     def channel_decay_attention(self, h: torch.Tensor, c: ChannelDecayAttentionConfig, w: dict, state: str, eps: float, out: torch.Tensor):
         """h [M, width] -> out f32 [M, width].  w: win [2 H dim + 2 H vdim + rank, width] (q | k | v | output gate | decay latent),
-        a2 [1, H dim, rank] and a2_b f32 [H dim] (the decay input's up-projection, run on the f32 latent), norm f32 [vdim],
-        o [width, H vdim].  Per head S <- diag(alpha) S + k v^T, alpha = sigmoid(z)^(1/tau), read out by q dim^(-1/2)."""
+        a2 [H dim, rank] and a2_b f32 [H dim] (the decay input's up-projection, applied to the f32 latent in the scan's first launch),
+        norm f32 [vdim], o [width, H vdim].  Per head S <- diag(alpha) S + k v^T, alpha = sigmoid(z)^(1/tau), read out by q dim^(-1/2)."""
         M, H, d, dv = self.M, c.heads, c.dim, c.vdim
         gcol = 2 * H * d + H * dv
         acol = gcol + H * dv
-        raw = self.linear(h, w["win"], self.buf("cd.raw", M, w["win"].shape[0]))
-        z = self.block_linear(raw, w["a2"], self.buf("cd.z", M, H * d), bias=w["a2_b"], exact=True, col=acol)
+        rank = w["a2"].shape[1]
+        assert w["win"].shape[0] == acol + rank and w["a2"].shape[0] == H * d
+        raw = self.linear(h, w["win"], self.buf("cd.raw", M, acol + rank))
         y = self.buf("cd.y", M, H * dv)
         ws = self.buf("cd.ws", M, -(-(H * d) // 4) * 4)
         self._op(K_MSTATE_SCAN, M=M, N=H * dv, taps=2, i0=H, i1=H, i2=d, cin=dv, K=H * d, a_rows=2 * H * d, A=raw, lda=raw.shape[1],
-                 res=z, ldr=z.shape[1], col_mod=0, f0=float(d) ** -0.5, f1=1.0 / float(c.tau), p0=self.slot.cur[state], C2=self.slot.next[state],
-                 C=y, ldc=y.shape[1], ws=ws, ws_bytes=ws.numel() * 4, flags=F_OUT_F32)
+                 res=raw, ldr=raw.shape[1], col_mod=acol, m_begin=rank, B=w["a2"], bias=w["a2_b"], f0=float(d) ** -0.5, f1=1.0 / float(c.tau),
+                 p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1], ws=ws, ws_bytes=ws.numel() * 4,
+                 flags=F_OUT_F32 | (F_F32 if w["a2"].dtype == torch.float32 else 0))
         yn = self.group_norm(y, w["norm"], H, eps, self.buf("cd.yn", M, H * dv, self.adt), n=H * dv, gate=raw, gate_col=gcol, weight_period=dv)
         return self.linear(yn, w["o"], out)
 

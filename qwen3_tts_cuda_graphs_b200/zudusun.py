@@ -121,7 +121,7 @@ class Packer:
 
     def channel_decay(self, p: str, m: ChannelDecayAttentionConfig) -> dict:
         raw, W, F = self.raw, self.W, self.F
-        return {"win": W(torch.cat([raw(p + n) for n in ("q", "k", "v", "g", "a1")], 0)), "a2": W(raw(p + "a2")[None]), "a2_b": F(raw(p + "a2.b")),
+        return {"win": W(torch.cat([raw(p + n) for n in ("q", "k", "v", "g", "a1")], 0)), "a2": W(raw(p + "a2")), "a2_b": F(raw(p + "a2.b")),
                 "norm": F(raw(p + "norm")), "o": W(raw(p + "o"))}
 
     def retention(self, p: str, m: RetentionConfig) -> dict:

@@ -80,7 +80,7 @@ def test_packing_and_state_declaration_follow_the_layers():
     left, right = m.layers[0]["mix"]["left"], m.layers[0]["mix"]["right"]
     assert torch.equal(left["wqkv"], torch.cat([W["l0.mix.left.q"], W["l0.mix.left.k"], W["l0.mix.left.v"]])) and left["sink"] is None
     assert torch.equal(right["win"], torch.cat([W[f"l0.mix.right.{n}"] for n in ("q", "k", "v", "g", "a1")]))
-    assert right["a2"].shape == (1, 30, 3) and torch.equal(right["a2"][0], W["l0.mix.right.a2"])
+    assert right["a2"].shape == (30, 3) and torch.equal(right["a2"], W["l0.mix.right.a2"])
     assert torch.allclose(m.layers[0]["sum_w"], torch.tensor([1.0, 0.7, 1.3, 1.0]))
     assert torch.allclose(m.layers[2]["sum_w"], torch.tensor([1.0, 1.0]))
     att = m.layers[1]["mix"]
@@ -102,7 +102,7 @@ def test_packing_and_state_declaration_follow_the_layers():
     del loose["layers"][2]["mixer"]["right"]["rank"]
     W2 = cases.weights(loose, rank=7)
     m2 = ZudusunModel(sequence_config_from_dict(loose), W2.get, "cpu")
-    assert m2.layers[2]["mix"]["right"]["a2"].shape == (1, 9, 7)
+    assert m2.layers[2]["mix"]["right"]["a2"].shape == (9, 7)
     with pytest.raises(ValueError):
         ZudusunModel(sequence_config_from_dict(loose), {**W2, "l2.mix.right.a1": W2["l2.mix.right.a1"][:-1]}.get, "cpu")
 
