@@ -168,7 +168,10 @@ enum fq3c_kind {
    *     rows res; z = B lat + bias with B [i0 * i2, m_begin] (bf16; FQ3C_F32: f32) and bias f32 [i0 * i2] or NULL, formed in the first
    *     launch; alpha = sigmoid(z)^f1 = exp(-f1 softplus(-z));  S <- diag(alpha) S + k v^T;  o = f0 S^T q;  i1 = i0;
    *     ws = f32 [M, round_up(i0 * i2, 4)] (the decays).
-   *     taps = 3 (retention: one fixed decay per head): same columns; S <- scale[h] S + (f0 k) v^T;  o = S^T q; no ws, no res.   */
+   *     taps = 3 (retention: one fixed decay per head): same columns; S <- scale[h] S + (f0 k) v^T;  o = S^T q; no res.
+   *     taps 1-3, M >= 512: when ws has room behind the per-row coefficients (rounded up to four floats) for P pieces' states and
+   *     decay products, P * i0 * i2 * (cin + 1) floats with 2 <= P <= 16, the rows are cut into P pieces that are walked side by
+   *     side, twice (own contribution from zero; start states by a carry pass; outputs): same sums in another order.              */
 };
 
 enum fq3c_flags {

@@ -1313,7 +1313,6 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
         fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
         count_launches(1);
       }
-      dim3 grid((o.cin + MS_COLS - 1) / MS_COLS, o.i0);
       static bool sattr[64] = {};
       int dev = 0;
       cudaGetDevice(&dev);
@@ -1325,19 +1324,45 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
         cudaFuncSetAttribute(fq3s_mstate_scan_kernel<64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         sattr[dev] = true;
       }
-      if (o.taps == 2) {
-        if (o.i2 <= 32) fq3s_mstate_scan_kernel<4, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4, 3), s>>>(o);
-        else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8, 3), s>>>(o);
-        else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16, 3), s>>>(o);
-        else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32, 3), s>>>(o);
-        else fq3s_mstate_scan_kernel<64, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64, 3), s>>>(o);
+      // Long runs of a recurrence whose decays do not depend on the state: pieces walked twice (see the kernel), when the caller's
+      // workspace has room behind the per-row coefficients for the pieces' states and decay products.
+      const int64_t base = o.taps == 3 ? 0 : ((int64_t)o.M * (o.taps == 2 ? mstate_decay_cols(o.i0, o.i2) : mstate_ws_cols(o.i0, o.i1, o.i2, false)) + 3) & ~(int64_t)3;
+      const int64_t per_piece = (int64_t)o.i0 * o.i2 * (o.cin + 1);
+      int pieces = 1, piece = o.M;
+      if (o.taps != 0 && o.M >= 512 && o.ws) {
+        pieces = (int)std::min<int64_t>(std::min(16, o.M / 128), (o.ws_bytes / 4 - base) / per_piece);
+        if (pieces >= 2) {
+          piece = (((o.M + pieces - 1) / pieces) + MS_CH - 1) / MS_CH * MS_CH;
+          pieces = (o.M + piece - 1) / piece;
+        }
+        if (pieces < 2) { pieces = 1; piece = o.M; }
+      }
+      float* X = pieces > 1 ? reinterpret_cast<float*>(o.ws) + base : nullptr;
+      float* P = pieces > 1 ? X + (int64_t)pieces * o.i0 * o.i2 * o.cin : nullptr;
+      const dim3 tiles((o.cin + MS_COLS - 1) / MS_COLS, o.i0);
+      auto walk = [&](const int phase, const int nz) {
+        const dim3 grid(tiles.x, tiles.y, nz);
+        if (o.taps == 2) {
+          if (o.i2 <= 32) fq3s_mstate_scan_kernel<4, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4, 3), s>>>(o, phase, piece, X, P);
+          else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8, 3), s>>>(o, phase, piece, X, P);
+          else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16, 3), s>>>(o, phase, piece, X, P);
+          else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32, 3), s>>>(o, phase, piece, X, P);
+          else fq3s_mstate_scan_kernel<64, 3><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64, 3), s>>>(o, phase, piece, X, P);
+        } else if (o.i2 <= 32) fq3s_mstate_scan_kernel<4><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4), s>>>(o, phase, piece, X, P);
+        else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8), s>>>(o, phase, piece, X, P);
+        else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16), s>>>(o, phase, piece, X, P);
+        else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32), s>>>(o, phase, piece, X, P);
+        else fq3s_mstate_scan_kernel<64><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64), s>>>(o, phase, piece, X, P);
+      };
+      if (pieces == 1) {
+        walk(0, 1);
         return 0;
       }
-      if (o.i2 <= 32) fq3s_mstate_scan_kernel<4><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4), s>>>(o);
-      else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8), s>>>(o);
-      else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16), s>>>(o);
-      else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32), s>>>(o);
-      else fq3s_mstate_scan_kernel<64><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64), s>>>(o);
+      walk(1, pieces - 1);
+      const int64_t n = (int64_t)o.i0 * o.i2 * o.cin;
+      fq3s_mstate_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(o, pieces, X, P);
+      walk(3, pieces);
+      count_launches(2);
       return 0;
     }
     case FQ3C_SUM_NORM: {

@@ -1891,8 +1891,14 @@ __host__ __device__ constexpr int mstate_buf_floats(int rpt, int nv = 2) { retur
 // of the token's key and query with 16-byte shared-memory loads (slices are padded apart by four floats: no bank conflicts),
 // and a product is finished by three shuffles.  The next round's tokens arrive by cp.async while the current round is walked.
 // NV = 3 (mode 2): a third staged vector per token, the decays of the head's key channels.
+//
+// A long run of rows of a recurrence whose decay does not depend on the state (modes 1-3) is cut into pieces of `piece` rows
+// (grid.z) and walked twice.  phase 1: every piece but the last starts from zero and leaves its own contribution S_loc in
+// X[z + 1] and the product of its decays per state row in P[z]; fq3s_mstate_carry_kernel then turns X into the states the pieces
+// start from (X[0] = the carried state, X[z + 1] = P[z] X[z] + S_loc[z]); phase 3: every piece walks again from X[z] and writes
+// the outputs, the last one also the next state.  phase 0: one pass over all rows (short runs, decoding, the delta rule).
 template <int RPT, int NV = 2>
-__global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) {
+__global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o, const int phase, const int piece, float* X, float* P) {
   extern __shared__ __align__(16) float msm[];
   constexpr int SL = RPT + 4, ROW = 8 * SL;
   const int H = o.i0, G = o.i1, dk = o.i2, dv = o.cin, h = blockIdx.y, g = h / (H / G);
@@ -1900,15 +1906,21 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const int wc = NV == 3 ? mstate_decay_cols(H, dk) : mstate_ws_cols(H, G, dk, delta);
   const int tid = threadIdx.x, sub = tid & 7, cl = tid >> 3, col = blockIdx.x * MS_COLS + cl;
   const bool live = col < dv;
+  const int zc = blockIdx.z, tb = phase == 0 ? 0 : zc * piece, te = phase == 0 ? o.M : min(o.M, tb + piece);
+  const bool last_piece = phase == 0 || te == o.M;
   constexpr int per = mstate_buf_floats(RPT, NV);
   {   // the padding between and behind the slices stays zero for the whole launch (only the token rows that will be used)
-    const int used = min(o.M, MS_CH) * NV * ROW;
+    const int used = min(te - tb, MS_CH) * NV * ROW;
     for (int i = tid; i < 2 * used; i += 128) msm[(i < used ? 0 : per - used) + i] = 0.f;
   }
   float S[RPT];
-  const float* st = reinterpret_cast<const float*>(o.p0) + (size_t)h * dk * dv;
+  float Pd[NV == 3 ? RPT : 1];       // phase 1: the product of the piece's decays (per state row, or one number per head)
 #pragma unroll
-  for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; S[r] = (live && i < dk) ? st[(size_t)i * dv + col] : 0.f; }
+  for (int r = 0; r < (NV == 3 ? RPT : 1); ++r) Pd[r] = 1.f;
+  const size_t hstate = (size_t)dk * dv;
+  const float* st = phase == 3 ? X + ((size_t)zc * H + h) * hstate : reinterpret_cast<const float*>(o.p0) + (size_t)h * hstate;
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; S[r] = (phase != 1 && live && i < dk) ? st[(size_t)i * dv + col] : 0.f; }
   const float D = (o.taps == 1 && o.B) ? reinterpret_cast<const float*>(o.B)[h] : 0.f;
   const float* wsb = reinterpret_cast<const float*>(o.ws);
   const float* rows = reinterpret_cast<const float*>(o.A);
@@ -1923,7 +1935,7 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
                    (NV < 3 || (wc % 4 == 0 && !(reinterpret_cast<uintptr_t>(wsb) & 15)));
   const float fixed_c1 = fixed ? reinterpret_cast<const float*>(o.scale)[h] : 0.f;
   auto fetch = [&](const int t0, float* buf) {
-    const int nt = min(MS_CH, o.M - t0);
+    const int nt = min(MS_CH, te - t0);
     float* kq = buf;
     float* vs = kq + MS_CH * NV * ROW;
     float* cf = vs + MS_CH * MS_COLS;
@@ -1960,11 +1972,11 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
       }
     cp_async_commit();
   };
-  fetch(0, msm);
+  fetch(tb, msm);
   int it = 0;
-  for (int t0 = 0; t0 < o.M; t0 += MS_CH, ++it) {
-    const int nt = min(MS_CH, o.M - t0);
-    if (t0 + MS_CH < o.M) {
+  for (int t0 = tb; t0 < te; t0 += MS_CH, ++it) {
+    const int nt = min(MS_CH, te - t0);
+    if (t0 + MS_CH < te) {
       fetch(t0 + MS_CH, msm + ((it + 1) & 1) * per);
       cp_async_wait<1>();
     } else {
@@ -1981,6 +1993,17 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
       float os[4] = {0.f, 0.f, 0.f, 0.f};       // four chains, so that a product's sum is not one long dependent row of multiply-adds
       if (NV == 3) {      // S <- diag(alpha) S + k v^T, o = f0 S^T q
         const float4* a4 = reinterpret_cast<const float4*>(kq + tt * NV * ROW + 2 * ROW + sub * SL);
+        if (phase == 1) {
+#pragma unroll
+          for (int r = 0; r < RPT / 4; ++r) {
+            const float4 kv = k4[r], av = a4[r];
+            S[4 * r] = fmaf(av.x, S[4 * r], kv.x * v); S[4 * r + 1] = fmaf(av.y, S[4 * r + 1], kv.y * v);
+            S[4 * r + 2] = fmaf(av.z, S[4 * r + 2], kv.z * v); S[4 * r + 3] = fmaf(av.w, S[4 * r + 3], kv.w * v);
+            constexpr int PR = NV == 3 ? 1 : 0;     // (this branch only runs with NV == 3; the index stays legal in the other instantiation)
+            Pd[PR * (4 * r)] *= av.x; Pd[PR * (4 * r + 1)] *= av.y; Pd[PR * (4 * r + 2)] *= av.z; Pd[PR * (4 * r + 3)] *= av.w;
+          }
+          continue;
+        }
 #pragma unroll
         for (int r = 0; r < RPT / 4; ++r) {
           const float4 kv = k4[r], qv = q4[r], av = a4[r];
@@ -2023,6 +2046,16 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
         }
         if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = fmaf(u, cf[tt * 4 + 2], c1 * qt);
         continue;
+      } else if (phase == 1) {
+        const float dx = c2 * v;
+#pragma unroll
+        for (int r = 0; r < RPT / 4; ++r) {
+          const float4 bv = k4[r];
+          S[4 * r] = fmaf(c1, S[4 * r], bv.x * dx); S[4 * r + 1] = fmaf(c1, S[4 * r + 1], bv.y * dx);
+          S[4 * r + 2] = fmaf(c1, S[4 * r + 2], bv.z * dx); S[4 * r + 3] = fmaf(c1, S[4 * r + 3], bv.w * dx);
+        }
+        Pd[0] *= c1;
+        continue;
       } else {
         const float dx = c2 * v;
 #pragma unroll
@@ -2043,9 +2076,34 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
     }
     __syncthreads();
   }
-  float* nst = reinterpret_cast<float*>(o.C2) + (size_t)h * dk * dv;
+  if (phase == 1) {       // this piece's own contribution becomes the next piece's start (after the carry pass); its decay product
+    float* nx = X + ((size_t)(zc + 1) * H + h) * hstate;
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; if (live && i < dk) nx[(size_t)i * dv + col] = S[r]; }
+    if (blockIdx.x == 0 && cl == 0) {
+      float* pz = P + ((size_t)zc * H + h) * dk;
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; if (i < dk) pz[i] = Pd[NV == 3 ? r : 0]; }
+    }
+    return;
+  }
+  if (!last_piece) return;
+  float* nst = reinterpret_cast<float*>(o.C2) + (size_t)h * hstate;
 #pragma unroll
   for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; if (live && i < dk) nst[(size_t)i * dv + col] = S[r]; }
+}
+
+// grid (ceil(H * dk * dv / 256)): X[0] = the carried state; X[z + 1] = P[z] X[z] + X[z + 1] for the pieces in order.
+__global__ void __launch_bounds__(256) fq3s_mstate_carry_kernel(const fq3c_op o, const int pieces, float* X, const float* P) {
+  const size_t n = (size_t)o.i0 * o.i2 * o.cin, e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const size_t hi = e / o.cin;        // (head, state row)
+  float R = reinterpret_cast<const float*>(o.p0)[e];
+  X[e] = R;
+  for (int z = 0; z + 1 < pieces; ++z) {
+    R = fmaf(P[(size_t)z * o.i0 * o.i2 + hi], R, X[(size_t)(z + 1) * n + e]);
+    X[(size_t)(z + 1) * n + e] = R;
+  }
 }
 
 // ===========================================================================================================================

@@ -344,10 +344,18 @@ class StepBuilder:
         return self.linear(oa, w["o"], out, bias=w.get("o_b"))
 
     # ---- recurrences with a matrix state per head -----------------------------------------------------
+    def _scan_ws(self, coef_cols: int, H: int, dk: int, dv: int, pieces: bool = True) -> torch.Tensor:
+        """Workspace of a matrix-state scan: per-row coefficients [M, coef_cols], and for a long run of rows (state-independent
+        decays only) room for up to 16 pieces' start states and decay products, which lets the library walk the pieces side by side."""
+        n = -(-(self.M * coef_cols) // 4) * 4
+        if pieces and self.M >= 512:
+            n += 16 * H * dk * (dv + 1)
+        return self.buf("ms.ws", 1, max(n, 4))
+
     def _mstate(self, mode: int, rows: torch.Tensor, raw: torch.Tensor, H: int, G: int, dk: int, dv: int, kcol: int, vcol: int,
                 decay_col: int, write_col: int, w: dict, state: str, y: torch.Tensor):
         wcols = -(-(2 * H + (2 * G * dk + G if mode == 0 else 0)) // 4) * 4      # rows padded to 16 bytes
-        ws = self.buf("ms.ws", self.M, wcols)
+        ws = self._scan_ws(wcols, H, dk, dv, pieces=mode != 0)
         kw = dict(M=self.M, N=H * dv, taps=mode, i0=H, i1=G, i2=dk, cin=dv, K=kcol, a_rows=vcol, A=rows, lda=rows.shape[1], res=raw,
                   ldr=raw.shape[1], col_mod=decay_col, m_begin=write_col, scale=w["A_log"], bias=w["dt_bias"],
                   p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1], ws=ws, ws_bytes=ws.numel() * 4, flags=F_OUT_F32)
@@ -390,7 +398,7 @@ class StepBuilder:
         assert w["win"].shape[0] == acol + rank and w["a2"].shape[0] == H * d
         raw = self.linear(h, w["win"], self.buf("cd.raw", M, acol + rank))
         y = self.buf("cd.y", M, H * dv)
-        ws = self.buf("cd.ws", M, -(-(H * d) // 4) * 4)
+        ws = self._scan_ws(-(-(H * d) // 4) * 4, H, d, dv)
         self._op(K_MSTATE_SCAN, M=M, N=H * dv, taps=2, i0=H, i1=H, i2=d, cin=dv, K=H * d, a_rows=2 * H * d, A=raw, lda=raw.shape[1],
                  res=raw, ldr=raw.shape[1], col_mod=acol, m_begin=rank, B=w["a2"], bias=w["a2_b"], f0=float(d) ** -0.5, f1=1.0 / float(c.tau),
                  p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1], ws=ws, ws_bytes=ws.numel() * 4,
@@ -409,8 +417,10 @@ class StepBuilder:
             self._op(K_ROT_APPEND, M=M, i0=2 * H, i1=0, i2=d, cin=0, taps=c.rot_dims, K=0, a_rows=0, A=raw, lda=raw.shape[1], B=w["freq"],
                      p0=self.slot.pos, flags=F_ROT_HALF)
         y = self.buf("rt.y", M, H * dv)
+        ws = self._scan_ws(0, H, d, dv)
         self._op(K_MSTATE_SCAN, M=M, N=H * dv, taps=3, i0=H, i1=H, i2=d, cin=dv, K=H * d, a_rows=2 * H * d, A=raw, lda=raw.shape[1],
-                 scale=w["decay"], f0=float(d) ** -0.5, p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1], flags=F_OUT_F32)
+                 scale=w["decay"], f0=float(d) ** -0.5, p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1],
+                 ws=ws, ws_bytes=ws.numel() * 4, flags=F_OUT_F32)
         yn = self.group_norm(y, None, H, eps, self.buf("rt.yn", M, H * dv, self.adt), n=H * dv, gate=raw, gate_col=gcol)
         return self.linear(yn, w["o"], out)
 

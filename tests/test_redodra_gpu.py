@@ -284,6 +284,28 @@ def test_state_space_scan_alone(H, P, N, G, taps, ng, f32):
     assert close_enough(got, want, f32), float(row_errors(got, want).max())
 
 
+@pytest.mark.parametrize("f32", [True, False])
+def test_state_space_scan_of_a_long_portion_walks_in_pieces(f32):
+    """Portions of 512 rows and more are cut into pieces that are walked side by side from start states a carry pass provides:
+    the answer is that of the row-by-row recurrence, also when the portion continues an earlier one."""
+    from qwen3_tts_cuda_graphs_b200.config import StateSpaceConfig
+    from qwen3_tts_cuda_graphs_b200.seq_state import StateSpec
+
+    H, P, N, G, taps, ng, width, T = 4, 24, 20, 2, 3, 2, 24, 1500
+    left = cases.attn_mixer(1, 1, 4, 4, 0.5, mask=(4, 0))
+    cfg = cases.config(8, width, [cases.layer(cases.parallel(left, cases.ssm(H, P, N, G, taps, ng)), None)], eps=1e-3)
+    W = {k[len("l0.mix.right."):]: v for k, v in cases.weights(cfg, seed=3).items() if k.startswith("l0.mix.right.")}
+    torch.manual_seed(8)
+    h = bf(torch.randn(T, width))
+    m = cfg["layers"][0]["mixer"]["right"]
+    want = ro.state_space_duality(h.to(F64), {k: v.to(F64) for k, v in W.items()}, "", m, 1e-3)
+    c = StateSpaceConfig(H, P, N, G, taps, ng)
+    bench = Bench([StateSpec("s.conv", "carry", H * P + 2 * G * N, taps - 1), StateSpec("s.s", "carry", P, H * N)], f32, max_pos=T + 3)
+    w = packer(W, f32).state_space("")
+    got = bench.portions(h, [37, 900, 2, 530], lambda b, rows, out: b.state_space(rows, c, w, "s", 1e-3, out), width)
+    assert close_enough(got, want, f32), float(row_errors(got, want).max())
+
+
 # ---------------------------------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------------------------------

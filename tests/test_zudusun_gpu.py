@@ -168,6 +168,10 @@ DECAY_CASES = {
     "wide_keys_many_value_tiles": (2, 136, 40, 4.0, 16, 64, 90, [64, 2, 20]),
     "keys_of_264_rows": (1, 264, 8, 32.0, 4, 32, 40, [17, 2]),
     "long_prompt_slow_decay": (4, 32, 64, 64.0, 16, 64, 400, [330, 2, 50]),
+    # portions of 512 rows and more are walked in pieces (side by side, from start states a carry pass provides)
+    "nine_pieces_ragged_tail_after_a_short_portion": (2, 20, 24, 32.0, 4, 32, 1300, [40, 1200, 2]),
+    "four_pieces_then_four_again": (3, 36, 8, 128.0, 2, 24, 1160, [600, 2, 550]),
+    "sixteen_pieces": (1, 12, 20, 256.0, 3, 16, 2200, [2150]),
 }
 
 
@@ -206,6 +210,9 @@ RETENTION_CASES = {
     "decay_one_and_decay_zero": (2, 8, 8, (1.0, 0.0), 8, 100.0, 16, 40, [20, 2]),
     "wide_heads_slow_decay": (4, 64, 32, (0.97, 0.98, 0.99, 0.999), 32, 1e5, 64, 400, [330, 2, 50]),
     "keys_of_144_rows": (1, 144, 20, (0.99,), 100, 1e4, 32, 60, [33, 2]),
+    # portions of 512 rows and more are walked in pieces
+    "six_pieces_after_a_short_portion": (2, 24, 20, (0.999, 0.97), 8, 1e4, 32, 900, [70, 777, 2]),
+    "sixteen_pieces_no_decay_at_all": (2, 8, 12, (1.0, 0.9995), 4, 100.0, 16, 2200, [2100, 2]),
 }
 
 
