@@ -1310,7 +1310,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
         return fail("mstate_scan: fixed decays need one value and one key head per head");
       }
       if (o.taps != 3) {
-        fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
+        fq3s_mstate_prep_kernel<<<o.taps == 2 ? (o.M + MS_PREP_ROWS - 1) / MS_PREP_ROWS : o.M, 128, 0, s>>>(o);
         count_launches(1);
       }
       static bool sattr[64] = {};

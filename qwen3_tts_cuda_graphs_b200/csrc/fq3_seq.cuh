@@ -1815,30 +1815,46 @@ __host__ __device__ inline int mstate_decay_cols(int H, int dk) { return (H * dk
 __host__ __device__ inline int mstate_ws_coef(int G, int dk, bool delta) { return delta ? 2 * G * dk : 0; }      // column of c1
 
 constexpr int MS_MAX_RANK = 1024;     // inner size of the decay projection (mode 2)
-// grid (M), 128 threads
+constexpr int MS_PREP_ROWS = 8;       // rows per block of the first launch in mode 2
+// grid (M), or (ceil(M / MS_PREP_ROWS)) in mode 2; 128 threads
 __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) {
   const int m = blockIdx.x, H = o.i0, G = o.i1, dk = o.i2;
   if (o.taps == 2) {
     // z = U lat + b with the row's decay latent lat (m_begin entries of the raw rows, f32) and U = B [H * dk, m_begin] (bf16, F32: f32):
-    // the up-projection is a few multiply-adds per channel, done here instead of in a product launch of its own.
+    // the up-projection is a few multiply-adds per channel, done here instead of in a product launch of its own.  A block takes
+    // MS_PREP_ROWS rows, so that an entry of U is loaded once for all of them (grid = ceil(M / MS_PREP_ROWS) in this mode).
     // alpha = sigmoid(z)^f1, through its logarithm -f1 softplus(-z): no underflow of the sigmoid on the way.
-    __shared__ float lat[MS_MAX_RANK];
-    const int R = o.m_begin;
-    const float* lr = reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr + o.col_mod;
-    for (int r = threadIdx.x; r < R; r += blockDim.x) lat[r] = lr[r];
+    __shared__ float lat[MS_PREP_ROWS][MS_MAX_RANK];
+    const int R = o.m_begin, m0 = blockIdx.x * MS_PREP_ROWS, nr = min(MS_PREP_ROWS, o.M - m0), cols = mstate_decay_cols(H, dk);
+    for (int i = threadIdx.x; i < MS_PREP_ROWS * R; i += blockDim.x) {
+      const int j = i / R, r = i - j * R;
+      lat[j][r] = j < nr ? reinterpret_cast<const float*>(o.res)[(size_t)(m0 + j) * o.ldr + o.col_mod + r] : 0.f;
+    }
     __syncthreads();
-    float* a = reinterpret_cast<float*>(o.ws) + (size_t)m * mstate_decay_cols(H, dk);
+    float* a = reinterpret_cast<float*>(o.ws) + (size_t)m0 * cols;
     const float* zb = reinterpret_cast<const float*>(o.bias);
     for (int c = threadIdx.x; c < H * dk; c += blockDim.x) {
-      float z = zb ? zb[c] : 0.f;
+      float z[MS_PREP_ROWS];
+#pragma unroll
+      for (int j = 0; j < MS_PREP_ROWS; ++j) z[j] = zb ? zb[c] : 0.f;
       if (o.flags & FQ3C_F32) {
         const float* u = reinterpret_cast<const float*>(o.B) + (size_t)c * R;
-        for (int r = 0; r < R; ++r) z = fmaf(lat[r], u[r], z);
+        for (int r = 0; r < R; ++r) {
+          const float uv = u[r];
+#pragma unroll
+          for (int j = 0; j < MS_PREP_ROWS; ++j) z[j] = fmaf(lat[j][r], uv, z[j]);
+        }
       } else {
         const bf16* u = reinterpret_cast<const bf16*>(o.B) + (size_t)c * R;
-        for (int r = 0; r < R; ++r) z = fmaf(lat[r], __bfloat162float(u[r]), z);
+        for (int r = 0; r < R; ++r) {
+          const float uv = __bfloat162float(u[r]);
+#pragma unroll
+          for (int j = 0; j < MS_PREP_ROWS; ++j) z[j] = fmaf(lat[j][r], uv, z[j]);
+        }
       }
-      a[c] = expf(-o.f1 * softplus_f(-z));
+#pragma unroll
+      for (int j = 0; j < MS_PREP_ROWS; ++j)
+        if (j < nr) a[(size_t)j * cols + c] = expf(-o.f1 * softplus_f(-z[j]));
     }
     return;
   }

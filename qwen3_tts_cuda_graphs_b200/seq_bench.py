@@ -82,9 +82,9 @@ def sizes():
 
     def zudusun(width, heads, kv, lin_heads, experts, top, expert_ff, shared_ff, order, window=1024, vocab=3072):
         left = SoftmaxAttentionConfig(heads // 2, max(1, kv // 2), 128, 128, 128 ** -0.5)
-        right = ChannelDecayAttentionConfig(lin_heads, 64, 128, 16.0, 16)
+        right = ChannelDecayAttentionConfig(lin_heads, 64, 128, 8.0, 32)
         att = SoftmaxAttentionConfig(heads, kv, 128, 128, 128 ** -0.5, rot_dims=64, rot_base=5e5, window=window, bias=True, qk_norm=True, zero_sink=True)
-        ret = RetentionConfig(lin_heads, 128, 128, tuple(1.0 - 2.0 ** (-5 - (8 * h) // lin_heads) for h in range(lin_heads)), rot_dims=128, rot_base=1e6)
+        ret = RetentionConfig(lin_heads, 128, 128, tuple(1.0 - 0.04 * 0.6 ** (8.0 * h / lin_heads) for h in range(lin_heads)), rot_dims=128, rot_base=2e5)
         mix = {"parallel": ScaledPairMixerConfig(left, right, 0.8, 0.5), "attention": att, "retention": ret}
         moe = MoEFFConfig(experts, 0, top, 1, 1, 1.0, expert_ff, shared_ff, act="relu2", router_bias=True, shared_gate=True)
         return ZudusunConfig(vocab, width, 1e-5, tuple(SeqLayerConfig(t, mix[t], moe) for t in order), tuple(range(len(order))))

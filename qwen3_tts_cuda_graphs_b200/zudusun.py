@@ -27,7 +27,7 @@ from .config import ChannelDecayAttentionConfig, MoEFFConfig, RetentionConfig, S
 from .seq_ops import StepBuilder
 from .seq_state import StateSpec
 
-SYNTHETIC_DECAY_RANK = 16      # init_synthetic's low-rank size when the configuration leaves it to the tensors
+SYNTHETIC_DECAY_RANK = 32      # init_synthetic's low-rank size when the configuration leaves it to the tensors
 
 
 def _attention_specs(p: str, m: SoftmaxAttentionConfig, W: int) -> Dict[str, tuple]:

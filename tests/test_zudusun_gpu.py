@@ -164,7 +164,7 @@ DECAY_CASES = {
     "five_heads_key_size_six": (5, 6, 3, 7.0, 3, 24, 70, [1, 2, 40, 17]),
     "one_head_wide_values": (1, 9, 37, 2.0, 5, 20, 45, [45]),
     "key_size_not_a_multiple_of_four": (3, 10, 16, 1.0, 2, 16, 33, [2, 2, 2]),
-    "two_rounds_of_state_rows": (2, 48, 24, 16.0, 8, 32, 120, [100, 3]),
+    "two_rounds_of_state_rows": (2, 44, 24, 12.0, 8, 32, 120, [100, 3]),
     "wide_keys_many_value_tiles": (2, 136, 40, 4.0, 16, 64, 90, [64, 2, 20]),
     "keys_of_264_rows": (1, 264, 8, 32.0, 4, 32, 40, [17, 2]),
     "long_prompt_slow_decay": (4, 32, 64, 64.0, 16, 64, 400, [330, 2, 50]),
@@ -208,7 +208,7 @@ RETENTION_CASES = {
     "all_of_the_head_turns": (2, 12, 5, (0.995, 0.8), 12, 50.0, 20, 45, [45]),
     "no_rotation": (2, 6, 9, (0.9, 0.5), 0, 1.0, 16, 33, [2, 2, 2]),
     "decay_one_and_decay_zero": (2, 8, 8, (1.0, 0.0), 8, 100.0, 16, 40, [20, 2]),
-    "wide_heads_slow_decay": (4, 64, 32, (0.97, 0.98, 0.99, 0.999), 32, 1e5, 64, 400, [330, 2, 50]),
+    "wide_heads_slow_decay": (4, 64, 48, (0.97, 0.98, 0.99, 0.999), 32, 1e5, 64, 400, [330, 2, 50]),
     "keys_of_144_rows": (1, 144, 20, (0.99,), 100, 1e4, 32, 60, [33, 2]),
     # portions of 512 rows and more are walked in pieces
     "six_pieces_after_a_short_portion": (2, 24, 20, (0.999, 0.97), 8, 1e4, 32, 900, [70, 777, 2]),
@@ -252,7 +252,7 @@ ATTENTION_CASES = {
     "one_key_head_full_rotation": (4, 1, 6, 10, 13, 6, 20, 45, [45], 3.0),
     "window_of_one": (2, 2, 6, 5, 1, 2, 16, 33, [2, 2, 2], 3.0),
     "window_wider_than_the_sequence": (3, 3, 4, 6, 400, 4, 16, 40, [40], 3.0),
-    "many_tiles_and_splits": (8, 2, 64, 32, 100, 24, 64, 330, [300, 2, 17], 5.0),
+    "many_tiles_and_splits": (8, 2, 64, 32, 100, 20, 64, 330, [300, 2, 17], 5.0),
     "window_edges_inside_tiles_and_portions": (4, 4, 16, 16, 37, 16, 32, 300, [36, 2, 91, 150], 5.0),
     "three_heads_per_key_head_no_rotation": (6, 2, 32, 16, 64, 0, 48, 200, [150, 2, 33], 4.0),
 }
@@ -336,6 +336,8 @@ MOE_CASES = {
     "an_expert_nobody_chooses": (6, 1, 10, 6, 16, 50),
     "single_token": (7, 4, 5, 3, 36, 1),
     "twenty_choices_of_forty": (40, 20, 6, 10, 32, 9),
+    "single_token_twenty_choices": (40, 20, 6, 10, 32, 1),
+    "hundred_and_thirty_experts": (130, 3, 4, None, 24, 21),
 }
 
 

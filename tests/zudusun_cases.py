@@ -70,7 +70,7 @@ def aligned():
     L = [
         layer(pair((8, 2, 64, 32, 0.125), (4, 32, 64, 8.0, 16), 0.6, 0.9), moe(4, 2, 64, 128)),
         layer(attn(8, 2, 32, 64, 70, 0.18, 16), moe(8, 1, 96, 64)),
-        layer(reten(4, 64, 32, (0.97, 0.98, 0.99, 0.995), 32, base=1e5), moe(3, 3, 32, None)),
+        layer(reten(4, 64, 48, (0.97, 0.98, 0.99, 0.995), 32, base=1e5), moe(3, 3, 32, None)),
         layer(attn(4, 4, 64, 32, 33, 0.125, 64, base=1000.0), None),
     ]
     L += [again(L, 1), again(L, 0), again(L, 2)]
