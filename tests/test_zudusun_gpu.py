@@ -614,6 +614,40 @@ def test_greedy_generation_through_engine_and_scheduler():
     eng.close_all()
 
 
+def test_command_line_continues_prompts_greedily_and_by_sampling(tmp_path, capsys):
+    """`cli lm` on a checkpoint on disk: greedy ids equal the oracle's argmax chain; the framework's sampler with top-k 1 is greedy,
+    and with a seed it repeats itself."""
+    import json
+
+    from qwen3_tts_cuda_graphs_b200 import cli
+
+    cfg = cases.odd()
+    W = cases.weights(cfg, seed=12)
+    cases.save_checkpoint(str(tmp_path), cfg, W)
+    prompts = [cases.tokens(cfg, L, seed=20 + i) for i, L in enumerate((12, 3, 27))]
+    n_new = 8
+    base = ["--dtype", "fp32", "lm", "--model", str(tmp_path), "--max-new-tokens", str(n_new), "--concurrency", "2", "--prefill-chunk", "5"]
+    for p in prompts:
+        base += ["--tokens", " ".join(str(t) for t in p)]
+
+    def run(extra):
+        capsys.readouterr()
+        cli.main(base + extra)
+        lines = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+        assert len(lines) == len(prompts) and all(d["finish"] == "length" and len(d["tokens"]) == n_new for d in lines)
+        return [d["tokens"] for d in lines]
+
+    greedy = run(["--greedy"])
+    for p, got in zip(prompts, greedy):
+        ids, margins = _oracle_greedy(cfg, W, p, n_new)
+        cut = next((i for i, m in enumerate(margins) if m < 1e-3), n_new)
+        assert cut >= 3 and got[:cut] == ids[:cut]
+    assert run(["--top-k", "1", "--seed", "5"]) == greedy
+    hot = run(["--temperature", "1.5", "--seed", "7"])
+    assert hot == run(["--temperature", "1.5", "--seed", "7"]) and all(0 <= t < cfg["vocab"] for row in hot for t in row)
+    assert hot != greedy
+
+
 def test_replayer_reads_a_checkpoint_from_disk_and_writes_the_wanted_logits(tmp_path):
     """bin/trace_run as a child process: the model class comes from config.json; a finished request's slot goes to the next."""
     import json
